@@ -2,8 +2,9 @@ from .base import ConfigError, ConfigReader, read_config_json, architecture_name
 from .hunyuan_dense import HunyuanDenseConfig
 from .pemezen import PemezenConfig
 from .novunex import NovunexConfig
+from .rutetar import RutetarConfig
 from .registry import (Architecture, register_architecture, get_architecture,
                        known_architectures, load_config)
 
-__all__ = ["ConfigError", "ConfigReader", "read_config_json", "architecture_name", "HunyuanDenseConfig", "PemezenConfig", "NovunexConfig",
+__all__ = ["ConfigError", "ConfigReader", "read_config_json", "architecture_name", "HunyuanDenseConfig", "PemezenConfig", "NovunexConfig", "RutetarConfig",
            "Architecture", "register_architecture", "get_architecture", "known_architectures", "load_config"]

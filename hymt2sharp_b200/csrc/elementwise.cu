@@ -129,6 +129,34 @@ __global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
 
 inline unsigned blocks_for(size_t total) { return (unsigned)((total + 255) / 256); }
 
+// out[r, c] = act(gu[r, c]) * gu[r, width + c] on rows that hold a gate half and an up half side by side; act: 0 silu,
+// 1 the tanh form of GELU.  A thread takes V neighbouring columns.
+template <typename T, int V>
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int width, int kind, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (i >= total) return;
+    const size_t r = i / width;
+    const int c = (int)(i - r * width);
+    const Pack<T, V> g = load_pack<T, V>(gu + r * 2 * width + c), u = load_pack<T, V>(gu + r * 2 * width + width + c);
+    Pack<T, V> o;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        const float z = to_float(g.v[k]);
+        const float a = kind == 0 ? z / (1.0f + expf(-z)) : gelu_tanh_f(z);
+        o.v[k] = from_float<T>(a * to_float(u.v[k]));
+    }
+    store_pack<T, V>(out + i, o);
+}
+
+__global__ void tanh_kernel(float* __restrict__ x, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = tanhf(x[i]);
+}
+
 }  // namespace
 
 HYMT2_API int hymt2_bias_act(void* x, int dtype, const float* bias, int rows, int cols, long ld, int act_cols, cudaStream_t stream) {
@@ -199,4 +227,25 @@ HYMT2_API int hymt2_softcap(float* x, float cap, long total, cudaStream_t stream
     HYMT2_REQUIRE(total > 0 && cap > 0.f, "softcap: bad arguments");
     launch_pdl(softcap_kernel, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, x, cap, (size_t)total);
     return hymt2_check_launch("softcap");
+}
+
+HYMT2_API int hymt2_gated_act(void* out, const void* gate_up, int dtype, int rows, int width, int kind, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && width > 0 && (kind == 0 || kind == 1), "gated_act: bad arguments");
+    const size_t total = (size_t)rows * width;
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        constexpr int V = 16 / sizeof(T);
+        if (width % V == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0)
+            launch_pdl(gated_act_kernel<T, V>, dim3(blocks_for(total / V)), dim3(256), 0, stream, (T*)out, (const T*)gate_up, width, kind, total);
+        else
+            launch_pdl(gated_act_kernel<T, 1>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)out, (const T*)gate_up, width, kind, total);
+    });
+    return hymt2_check_launch("gated_act");
+}
+
+HYMT2_API int hymt2_tanh(float* x, long total, cudaStream_t stream) {
+    if (total == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(total > 0, "tanh: bad sizes");
+    launch_pdl(tanh_kernel, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, x, (size_t)total);
+    return hymt2_check_launch("tanh");
 }

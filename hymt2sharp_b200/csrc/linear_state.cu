@@ -1,0 +1,361 @@
+// Mixers whose memory is a matrix per head instead of a list of keys: S [dk, dv] float32 per (sequence, head), carried from
+// token to token and from step to step in the sequence's state row.
+//
+//   fixed decay    S = g_h S + (c k_t) v_t^T;                o_t = S^T q_t                    (g_h a constant of the head, c a constant)
+//   token decay    o_t = (S + diag(u_h) k_t v_t^T)^T r_t;    S = diag(w_t) S + k_t v_t^T      (w_t = exp(-exp(x_t + w0)) per channel)
+//
+// Both forms are independent per value column j of S, so a block owns a tile of columns of one (sequence, head) and a thread
+// one column: S[:, j] in registers where dk is one of the sizes compiled for, in shared memory otherwise.  Everything that
+// enters the recurrence is float32; q, k, v arrive in the engine's compute type.  The scan writes o as float32; the norm of
+// each head's o, the gain and the gate follow in `head_norm_gate`.
+//
+// Long portions run in three passes over chunks of CHUNK tokens instead of one serial walk (the recurrences compose):
+//   pass 1  per chunk, from a zero state: the chunk's own contribution B_c to the state, and the product A_c of its decays
+//   pass 2  per (sequence, head): the state at every chunk's start, S_c = A_(c-1) S_(c-1) + B_(c-1), serial over chunks
+//   pass 3  per chunk: the walk over its tokens from S_c, which writes o
+// so a prompt of thousands of tokens keeps the whole device busy.  The order of the sums inside a chunk is the serial one; the
+// state at a chunk's start is the same value in another association, which differs from the serial walk by rounding only.
+//
+// `token_shift`: the inputs of a time-mixing layer, m_s[t] = h[t] + (h[t-1] - h[t]) * mu_s for several s at once, with the last
+// h of the step before taken from (and the step's last h written to) the state row.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CHUNK = 64;          // tokens of a chunk of the three-pass form
+constexpr int MIN_CHUNKED = 192;   // a step whose longest portion has at least this many tokens runs in three passes
+
+struct ScanParams {
+    float* out;                    // [tokens][heads * dv] float32
+    const void* q;                 // q (fixed decay) or r (token decay): rows of heads * dk
+    const void* k;
+    const void* v;                 // rows of heads * dv
+    const float* x;                // token decay: [tokens][heads * dk] float32, the decay's inner exponent without w0
+    const float* w0;               // token decay: [heads * dk]
+    const float* u;                // token decay: [heads * dk] bonus
+    const float* decay;            // fixed decay: [heads]
+    float k_scale;                 // fixed decay: keys are multiplied by this
+    long ldq, ldk, ldv, ldx;       // row strides in elements
+    uint8_t* state;                // the cache's state rows
+    long state_offset, state_stride;   // bytes
+    const int* cu_seqlens;
+    const int* slot_ids;
+    const int* kv_lens;
+    int heads, dk, dv;
+    // the three-pass form
+    float* chunk_B;                // [chunks][heads][dk][dv]
+    float* chunk_A;                // token decay: [chunks][heads][dk] products of decays; fixed decay: unused
+    const int* chunk_seq;          // [chunks] sequence of a chunk
+    const int* chunk_first;        // [chunks] first token (row) of a chunk
+    const int* chunk_len;          // [chunks]
+    const int* seq_chunk0;         // [sequences + 1] first chunk of a sequence
+};
+
+// One thread's walk over `n` tokens for its column j of one head.  MODE 0: fixed decay, 1: token decay.
+// WRITE_OUT: o is written; the state goes from S (in/out).  `vecs` is shared memory for two tokens' vectors.
+template <typename T, int MODE, int DK, bool WRITE_OUT>
+__device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool live, int row0, int n, float* S, int sstride,
+                                     float* vecs, float gh) {
+    const int dk = DK > 0 ? DK : p.dk;
+    const int nvec = MODE == 0 ? 2 : 3;              // q, k (, w) per token
+    const T* q = (const T*)p.q + (size_t)head * dk;
+    const T* k = (const T*)p.k + (size_t)head * dk;
+    const T* v = (const T*)p.v + (size_t)head * p.dv;
+    auto stage = [&](int t, float* dst) {
+        const size_t r = (size_t)(row0 + t);
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+            dst[i] = to_float(q[r * p.ldq + i]);
+            const float kk = to_float(k[r * p.ldk + i]);
+            dst[dk + i] = MODE == 0 ? kk * p.k_scale : kk;
+            if (MODE == 1) dst[2 * dk + i] = expf(-expf(p.x[r * p.ldx + (size_t)head * dk + i] + p.w0[(size_t)head * dk + i]));
+        }
+    };
+    const float* uu = MODE == 1 ? p.u + (size_t)head * dk : nullptr;
+    stage(0, vecs);
+    __syncthreads();
+    for (int t = 0; t < n; t++) {
+        float* cur = vecs + (size_t)(t & 1) * nvec * dk;
+        if (t + 1 < n) stage(t + 1, vecs + (size_t)((t + 1) & 1) * nvec * dk);
+        const float vj = live ? to_float(v[(size_t)(row0 + t) * p.ldv + j]) : 0.f;
+        float acc = 0.f;
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < (DK > 0 ? DK : 1); i++) {
+                if (MODE == 0) {
+                    S[i] = fmaf(gh, S[i], cur[dk + i] * vj);
+                    acc = fmaf(S[i], cur[i], acc);
+                } else {
+                    const float kv = cur[dk + i] * vj;
+                    acc = fmaf(cur[i], fmaf(uu[i], kv, S[i]), acc);
+                    S[i] = fmaf(cur[2 * dk + i], S[i], kv);
+                }
+            }
+        } else {
+            for (int i = 0; i < dk; i++) {
+                float s = S[(size_t)i * sstride];
+                if (MODE == 0) {
+                    s = fmaf(gh, s, cur[dk + i] * vj);
+                    acc = fmaf(s, cur[i], acc);
+                } else {
+                    const float kv = cur[dk + i] * vj;
+                    acc = fmaf(cur[i], fmaf(uu[i], kv, s), acc);
+                    s = fmaf(cur[2 * dk + i], s, kv);
+                }
+                S[(size_t)i * sstride] = s;
+            }
+        }
+        if (WRITE_OUT && live) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = acc;
+        __syncthreads();
+    }
+}
+
+// PASS 0: the serial form, grid (column tiles, heads, sequences).  PASS 1 and 3: grid (column tiles, heads, chunks).
+template <typename T, int MODE, int DK, int PASS>
+__global__ void __launch_bounds__(128)
+scan_kernel(ScanParams p) {
+    extern __shared__ float smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int dk = DK > 0 ? DK : p.dk;
+    const int nvec = MODE == 0 ? 2 : 3;
+    float* vecs = smem;                                   // [2][nvec][dk]
+    float* shared_state = smem + 2 * nvec * dk;           // [dk][blockDim.x] when DK == 0
+    const int head = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = j < p.dv;
+    int seq, row0, n, chunk = 0;
+    bool from_zero, keep;
+    if (PASS == 0) {
+        seq = blockIdx.z;
+        row0 = p.cu_seqlens[seq];
+        n = p.cu_seqlens[seq + 1] - row0;
+        from_zero = p.kv_lens[seq] - n == 0;
+        keep = true;
+    } else {
+        chunk = blockIdx.z;
+        seq = p.chunk_seq[chunk];
+        row0 = p.chunk_first[chunk];
+        n = p.chunk_len[chunk];
+        from_zero = PASS == 1;
+        keep = false;
+    }
+    if (n <= 0) return;
+    const int slot = p.slot_ids[seq];
+    if (slot < 0) {                                       // a padding row: zeros out, nothing remembered
+        if (PASS != 1 && live)
+            for (int t = 0; t < n; t++) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = 0.f;
+        return;
+    }
+    float* st = reinterpret_cast<float*>(p.state + (size_t)slot * p.state_stride + p.state_offset) + (size_t)head * dk * p.dv;
+    const float* from = PASS == 3 ? p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv : st;   // pass 2 left S_c in chunk_B
+    float reg[DK > 0 ? DK : 1];
+    float* S = DK > 0 ? reg : shared_state + threadIdx.x;
+    const int sstride = DK > 0 ? 1 : blockDim.x;
+    for (int i = 0; i < dk; i++) S[(size_t)i * sstride] = (!from_zero && live) ? from[(size_t)i * p.dv + j] : 0.f;
+    const float gh = MODE == 0 ? p.decay[head] : 0.f;
+    if (PASS == 1) walk<T, MODE, DK, false>(p, head, j, live, row0, n, S, sstride, vecs, gh);
+    else walk<T, MODE, DK, true>(p, head, j, live, row0, n, S, sstride, vecs, gh);
+    if (PASS == 1) {
+        float* B = p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv;
+        if (live)
+            for (int i = 0; i < dk; i++) B[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+        if (MODE == 1 && blockIdx.x == 0) {               // the product of the chunk's decays per channel, in token order
+            float* A = p.chunk_A + ((size_t)chunk * p.heads + head) * dk;
+            for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+                float a = 1.f;
+                for (int t = 0; t < n; t++)
+                    a *= expf(-expf(p.x[(size_t)(row0 + t) * p.ldx + (size_t)head * dk + i] + p.w0[(size_t)head * dk + i]));
+                A[i] = a;
+            }
+        }
+    } else if (keep && live) {
+        for (int i = 0; i < dk; i++) st[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+    }
+}
+
+// Pass 2: S at every chunk's start.  A thread owns one entry (i, j) of one (sequence, head) and walks the sequence's chunks:
+// chunk_B[c] holds B_c on entry and S_c (the state in FRONT of chunk c) on exit; the state row receives the state behind the
+// last chunk.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+scan_carry_kernel(ScanParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int per = p.dk * p.dv;
+    if (e >= per) return;
+    const int slot = p.slot_ids[seq];
+    const int c0 = p.seq_chunk0[seq], c1 = p.seq_chunk0[seq + 1];
+    if (slot < 0 || c1 <= c0) return;
+    const int n = p.cu_seqlens[seq + 1] - p.cu_seqlens[seq];
+    float* st = reinterpret_cast<float*>(p.state + (size_t)slot * p.state_stride + p.state_offset) + (size_t)head * per;
+    float s = p.kv_lens[seq] - n == 0 ? 0.f : st[e];
+    const int i = e / p.dv;
+    const float gh = MODE == 0 ? p.decay[head] : 0.f;
+    for (int c = c0; c < c1; c++) {
+        float* B = p.chunk_B + ((size_t)c * p.heads + head) * per;
+        const float b = B[e];
+        B[e] = s;
+        float a;
+        if (MODE == 0) {
+            a = 1.f;
+            const int len = p.chunk_len[c];
+            for (int t = 0; t < len; t++) a *= gh;
+        } else {
+            a = p.chunk_A[((size_t)c * p.heads + head) * p.dk + i];
+        }
+        s = fmaf(a, s, b);
+    }
+    st[e] = s;
+}
+
+// out[t, head, :] = o[t, head, :] / sqrt(mean(o^2) + eps) * (weight[head, :] if given) * act(gate[t, head, :]), a warp per
+// (token, head); act: 0 none (no gate), 1 silu.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, long ldg, const float* __restrict__ weight,
+                      long items, int heads, int dv, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const long t = item / heads;
+    const int head = (int)(item % heads);
+    const float* row = o + (size_t)item * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(row[c], row[c], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)dv + eps);
+    for (int c = lane; c < dv; c += 32) {
+        float y = row[c] * r;
+        if (weight) y *= weight[(size_t)head * dv + c];
+        if (gate) {
+            const float g = to_float(gate[(size_t)t * ldg + (size_t)head * dv + c]);
+            y *= g / (1.0f + expf(-g));
+        }
+        out[(size_t)item * dv + c] = from_float<T>(y);
+    }
+}
+
+// mixes[t][s * width + c] = h[t][c] + (h[t-1][c] - h[t][c]) * mu[s][c]; a sequence's first new token takes h[t-1] from the state
+// row (zeros at position 0), and the thread of that token also writes the step's last h there: one thread reads and renews.
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(T* __restrict__ mixes, const T* __restrict__ h, long ldh, const float* __restrict__ mu, int count, uint8_t* state,
+                   long state_offset, long state_stride, const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                   const int* __restrict__ slot_ids, const int* __restrict__ kv_lens, int tokens, int width) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)tokens * width) return;
+    const int t = (int)(idx / width), c = (int)(idx % width);
+    const int seq = token_seq[t];
+    const int first = cu_seqlens[seq], last = cu_seqlens[seq + 1] - 1;
+    const float cur = to_float(h[(size_t)t * ldh + c]);
+    float prev;
+    if (t > first) {
+        prev = to_float(h[(size_t)(t - 1) * ldh + c]);
+    } else {
+        const int slot = slot_ids[seq];
+        prev = 0.f;
+        if (slot >= 0) {
+            float* st = reinterpret_cast<float*>(state + (size_t)slot * state_stride + state_offset);
+            const bool at_start = kv_lens[seq] - (last - first + 1) == 0;
+            if (!at_start) prev = st[c];
+            st[c] = to_float(h[(size_t)last * ldh + c]);
+        }
+    }
+    for (int s = 0; s < count; s++)
+        mixes[(size_t)t * count * width + (size_t)s * width + c] = from_float<T>(fmaf(prev - cur, mu[(size_t)s * width + c], cur));
+}
+
+template <typename T, int MODE, int DK, int PASS>
+int launch_scan(const ScanParams& p, int tiles, int threads, int z, cudaStream_t stream) {
+    const int dk = p.dk, nvec = MODE == 0 ? 2 : 3;
+    const size_t smem = ((size_t)2 * nvec * dk + (DK > 0 ? 0 : (size_t)dk * threads)) * sizeof(float);
+    if (smem > 48 * 1024) {
+        HYMT2_REQUIRE(smem <= 200 * 1024, "linear_scan: heads of %d key entries are too large", dk);
+        cudaFuncSetAttribute(scan_kernel<T, MODE, DK, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    launch_pdl(scan_kernel<T, MODE, DK, PASS>, dim3(tiles, p.heads, z), dim3(threads), smem, stream, p);
+    return HYMT2_OK;
+}
+
+template <typename T, int MODE, int PASS>
+int launch_scan_dk(const ScanParams& p, int z, cudaStream_t stream) {
+    // columns a block: enough blocks to fill the device matter more than wide blocks
+    const int threads = p.dv >= 64 ? 64 : 32;
+    const int tiles = (p.dv + threads - 1) / threads;
+    switch (p.dk) {
+        case 16: return launch_scan<T, MODE, 16, PASS>(p, tiles, threads, z, stream);
+        case 32: return launch_scan<T, MODE, 32, PASS>(p, tiles, threads, z, stream);
+        case 64: return launch_scan<T, MODE, 64, PASS>(p, tiles, threads, z, stream);
+        case 128: return launch_scan<T, MODE, 128, PASS>(p, tiles, threads, z, stream);
+        default: return launch_scan<T, MODE, 0, PASS>(p, tiles, threads, z, stream);
+    }
+}
+
+}  // namespace
+
+// Floats and ints of scratch that the three-pass form needs for a step of `chunks` chunks (0: the step runs serially).
+HYMT2_API int hymt2_linear_scan_chunk() { return CHUNK; }
+HYMT2_API int hymt2_linear_scan_min_chunked() { return MIN_CHUNKED; }
+
+// mode 0: fixed decay per head (decay [heads], k_scale); mode 1: decay per token and channel with a bonus (x, w0, u).
+// chunks > 0: the three-pass form over the chunks that the host laid out (chunk_* and seq_chunk0 int32 on the device, chunk_B
+// [chunks * heads * dk * dv] and chunk_A [chunks * heads * dk] float32 scratch).
+HYMT2_API int hymt2_linear_scan(float* out, const void* q, const void* k, const void* v, int dtype, long ldq, long ldk, long ldv,
+                                const float* x, long ldx, const float* w0, const float* u, const float* decay, float k_scale, int mode,
+                                uint8_t* state, long state_offset, long state_stride, const int* cu_seqlens, const int* slot_ids,
+                                const int* kv_lens, int batch, int heads, int dk, int dv, int chunks, float* chunk_B, float* chunk_A,
+                                const int* chunk_seq, const int* chunk_first, const int* chunk_len, const int* seq_chunk0,
+                                cudaStream_t stream) {
+    if (batch == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(batch > 0 && heads > 0 && dk > 0 && dv > 0, "linear_scan: bad sizes");
+    HYMT2_REQUIRE(mode == 0 || mode == 1, "linear_scan: unknown mode %d", mode);
+    HYMT2_REQUIRE(mode == 0 ? decay != nullptr : (x && w0 && u), "linear_scan: the decay's tensors are missing");
+    HYMT2_REQUIRE(chunks == 0 || (chunk_B && chunk_seq && chunk_first && chunk_len && seq_chunk0 && (mode == 0 || chunk_A)),
+                  "linear_scan: the chunked form needs its scratch");
+    ScanParams p{out, q, k, v, x, w0, u, decay, k_scale, ldq, ldk, ldv, ldx, state, state_offset, state_stride, cu_seqlens, slot_ids,
+                 kv_lens, heads, dk, dv, chunk_B, chunk_A, chunk_seq, chunk_first, chunk_len, seq_chunk0};
+    int rc = HYMT2_OK;
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        if (chunks == 0) {
+            rc = mode == 0 ? launch_scan_dk<T, 0, 0>(p, batch, stream) : launch_scan_dk<T, 1, 0>(p, batch, stream);
+        } else {
+            rc = mode == 0 ? launch_scan_dk<T, 0, 1>(p, chunks, stream) : launch_scan_dk<T, 1, 1>(p, chunks, stream);
+            if (rc == HYMT2_OK) {
+                const int per = dk * dv;
+                if (mode == 0) launch_pdl(scan_carry_kernel<0>, dim3((per + 255) / 256, heads, batch), dim3(256), 0, stream, p);
+                else launch_pdl(scan_carry_kernel<1>, dim3((per + 255) / 256, heads, batch), dim3(256), 0, stream, p);
+                rc = mode == 0 ? launch_scan_dk<T, 0, 3>(p, chunks, stream) : launch_scan_dk<T, 1, 3>(p, chunks, stream);
+            }
+        }
+    });
+    if (rc != HYMT2_OK) return rc;
+    return hymt2_check_launch("linear_scan");
+}
+
+HYMT2_API int hymt2_head_norm_gate(void* out, const float* o, const void* gate, long ldg, int dtype, const float* weight, int tokens,
+                                   int heads, int dv, float eps, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && heads > 0 && dv > 0, "head_norm_gate: bad sizes");
+    const long items = (long)tokens * heads;
+    HYMT2_DISPATCH_DTYPE(dtype, T, (launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, o,
+                                               (const T*)gate, ldg, weight, items, heads, dv, eps)));
+    return hymt2_check_launch("head_norm_gate");
+}
+
+HYMT2_API int hymt2_token_shift(void* mixes, const void* h, long ldh, int dtype, const float* mu, int count, uint8_t* state,
+                                long state_offset, long state_stride, const int* token_seq, const int* cu_seqlens, const int* slot_ids,
+                                const int* kv_lens, int tokens, int width, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && width > 0 && count > 0, "token_shift: bad sizes");
+    const long items = (long)tokens * width;
+    HYMT2_DISPATCH_DTYPE(dtype, T, (launch_pdl(token_shift_kernel<T>, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream, (T*)mixes,
+                                               (const T*)h, ldh, mu, count, state, state_offset, state_stride, token_seq, cu_seqlens,
+                                               slot_ids, kv_lens, tokens, width)));
+    return hymt2_check_launch("token_shift");
+}

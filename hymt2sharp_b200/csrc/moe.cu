@@ -3,8 +3,9 @@
 // Everything here is float32 and integer arithmetic; nothing depends on the order in which blocks run (no atomics), so a
 // token's result does not depend on what else is in the step.
 //
-//   route    scores s = softmax(z) over ALL router outputs; the `top` largest of s + correction are chosen (ties: the
-//            lower index); a chosen output's weight is its s, without the correction and not renormalised
+//   route    scores s = softmax(z + bias) over ALL router outputs (bias: optional); the `top` largest of s + correction are
+//            chosen (ties: the lower index); a chosen output's weight is its s, without the correction, either as it is or
+//            (`renorm`) divided by the sum over the chosen ones, which is the softmax over the chosen outputs alone
 //   count    how many (token, choice) pairs name each expert that has tensors (outputs from `experts` on name identity
 //            experts, which need no product)
 //   place    every expert's pairs, in token order, get consecutive rows of a sorted list; an expert's segment is padded to
@@ -20,7 +21,7 @@ constexpr int ROUTE_WARPS = 4;
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
-                 const float* __restrict__ correction, int tokens, int outputs, int top) {
+                 const float* __restrict__ correction, const float* __restrict__ bias, int renorm, int tokens, int outputs, int top) {
     extern __shared__ float smem[];   // [ROUTE_WARPS][2 * outputs]: scores, choice scores
     pdl_wait();
     pdl_launch_dependents();
@@ -31,10 +32,10 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
     float* c = s + outputs;
     const float* z = logits + (size_t)t * outputs;
     float m = -INFINITY;
-    for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i]);
+    for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i] + (bias ? bias[i] : 0.f));
     m = warp_max(m);
     float sum = 0.f;
-    for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] - m); s[i] = e; sum += e; }
+    for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] + (bias ? bias[i] : 0.f) - m); s[i] = e; sum += e; }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
     for (int i = lane; i < outputs; i += 32) {
@@ -59,6 +60,11 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
             c[at] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (renorm && lane == 0) {   // the weights become the softmax over the chosen outputs alone: the same exponentials, another sum
+        float chosen_sum = 0.f;
+        for (int k = 0; k < top; k++) chosen_sum += weight[(size_t)t * top + k];
+        for (int k = 0; k < top; k++) weight[(size_t)t * top + k] /= chosen_sum;
     }
 }
 
@@ -184,7 +190,7 @@ constexpr int SMALL_PAIRS = 1024, SMALL_THREADS = 256;
 __global__ void __launch_bounds__(SMALL_THREADS)
 moe_route_place_small_kernel(int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ pair_row, int* __restrict__ row_token,
                              int* __restrict__ tile_group, const float* __restrict__ logits, const float* __restrict__ correction,
-                             int tokens, int outputs, int top, int experts, int tile, int max_tiles) {
+                             const float* __restrict__ bias, int renorm, int tokens, int outputs, int top, int experts, int tile, int max_tiles) {
     extern __shared__ float smem[];   // [warps][2 * outputs] scores and choice scores, then [experts + 1] segment starts
     __shared__ int pairs_s[SMALL_PAIRS];
     pdl_wait();
@@ -196,10 +202,10 @@ moe_route_place_small_kernel(int* __restrict__ chosen, float* __restrict__ weigh
     for (int t = warp; t < tokens; t += warps) {
         const float* z = logits + (size_t)t * outputs;
         float m = -INFINITY;
-        for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i]);
+        for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i] + (bias ? bias[i] : 0.f));
         m = warp_max(m);
         float sum = 0.f;
-        for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] - m); s[i] = e; sum += e; }
+        for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] + (bias ? bias[i] : 0.f) - m); s[i] = e; sum += e; }
         sum = warp_sum(sum);
         const float inv = 1.0f / sum;
         for (int i = lane; i < outputs; i += 32) {
@@ -225,6 +231,11 @@ moe_route_place_small_kernel(int* __restrict__ chosen, float* __restrict__ weigh
                 c[at] = -INFINITY;
             }
             __syncwarp();
+        }
+        if (renorm && lane == 0) {
+            float chosen_sum = 0.f;
+            for (int k = 0; k < top; k++) chosen_sum += weight[(size_t)t * top + k];
+            for (int k = 0; k < top; k++) weight[(size_t)t * top + k] /= chosen_sum;
         }
     }
     __syncthreads();
@@ -328,14 +339,14 @@ HYMT2_API int hymt2_moe_gather(void* xs, const void* x, int dtype, const int* ro
     return hymt2_check_launch("moe_gather");
 }
 
-HYMT2_API int hymt2_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int tokens, int outputs,
-                              int top, cudaStream_t stream) {
+HYMT2_API int hymt2_moe_route(int* chosen, float* weight, const float* logits, const float* correction, const float* bias, int renorm,
+                              int tokens, int outputs, int top, cudaStream_t stream) {
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && outputs > 0 && top > 0 && top <= outputs, "moe_route: bad sizes tokens=%d outputs=%d top=%d", tokens, outputs, top);
     const size_t smem = (size_t)ROUTE_WARPS * 2 * outputs * sizeof(float);
     HYMT2_REQUIRE(smem <= 48 * 1024, "moe_route: %d router outputs are too many", outputs);
     launch_pdl(moe_route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen, weight,
-               logits, correction, tokens, outputs, top);
+               logits, correction, bias, renorm, tokens, outputs, top);
     return hymt2_check_launch("moe_route");
 }
 
@@ -366,8 +377,8 @@ HYMT2_API int hymt2_moe_combine(float* out, const float* y, const void* x, int x
 
 // moe_route and moe_place in one launch for a step of few tokens (tokens * top <= 1024, experts <= 4096).
 HYMT2_API int hymt2_moe_route_place_small(int* chosen, float* weight, int* pair_row, int* row_token, int* tile_group, const float* logits,
-                                          const float* correction, int tokens, int outputs, int top, int experts, int tile, int max_tiles,
-                                          cudaStream_t stream) {
+                                          const float* correction, const float* bias, int renorm, int tokens, int outputs, int top, int experts,
+                                          int tile, int max_tiles, cudaStream_t stream) {
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && outputs > 0 && top > 0 && top <= outputs && experts >= 0 && experts <= outputs && tile > 0, "moe_route_place_small: bad sizes");
     HYMT2_REQUIRE((long)tokens * top <= SMALL_PAIRS, "moe_route_place_small: %d pairs are too many", tokens * top);
@@ -375,7 +386,7 @@ HYMT2_API int hymt2_moe_route_place_small(int* chosen, float* weight, int* pair_
     const size_t smem = ((size_t)(SMALL_THREADS / 32) * 2 * outputs + experts + 1) * sizeof(float);
     HYMT2_REQUIRE(smem <= 40 * 1024, "moe_route_place_small: %d router outputs are too many", outputs);
     launch_pdl(moe_route_place_small_kernel, dim3(1), dim3(SMALL_THREADS), smem, stream, chosen, weight, pair_row, row_token, tile_group,
-               logits, correction, tokens, outputs, top, experts, tile, max_tiles);
+               logits, correction, bias, renorm, tokens, outputs, top, experts, tile, max_tiles);
     return hymt2_check_launch("moe_route_place");
 }
 

@@ -23,6 +23,7 @@ class DecoderModel:
         self.groups: list[GroupSpec] = []
         self.slots: list[list[MixerSlot]] = []   # per entry of the order: one MixerSlot for each mixer of its block
         self.state_bytes = 0
+        self._ones = None
         # a step can be captured into a CUDA graph only if every part launches kernels and nothing else
         self.graph_safe = all(getattr(b, "graph_safe", False) for b in self.blocks)
         self._plan_memory()
@@ -88,6 +89,8 @@ class DecoderModel:
         for b in self.blocks:
             b.load(weights, device, dtype)
         self.final_norm.load(weights, device, dtype)
+        if s.residual_streams is not None:
+            self._ones = torch.ones(s.residual_streams, dtype=torch.float32, device=device)
         self.head = Linear(self.embedding if s.head is None else compute_form(weights[s.head], device, dtype), role="head")
         if dtype == torch.bfloat16:
             # a tensor stored in 32-bit stays so; for a MATRIX that means its product runs on the CUDA-core kernel,
@@ -131,15 +134,26 @@ class DecoderModel:
         """Runs the step's tokens through all layers; returns float32 logits [num_want, vocab]
         of the token rows that `want_rows` names (int32, device)."""
         T = ctx.num_tokens
-        residual = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
-        ops.embed(residual, self.embedding, ctx.tokens, ctx.status, self.spec.embed_scale or 1.0)
+        streams = self.spec.residual_streams
+        if streams is None:
+            residual = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
+            ops.embed(residual, self.embedding, ctx.tokens, ctx.status, self.spec.embed_scale or 1.0)
+        else:
+            residual = torch.empty((streams, T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
+            ops.embed(residual[0], self.embedding, ctx.tokens, ctx.status, self.spec.embed_scale or 1.0)
+            ops.streams_fill(residual)
         order = self.spec.order
         for i, (run, slots) in enumerate(zip(order, self.slots)):
             # the first norm of the block that runs next, for a block whose last product can prepare it (parts.base.Prenormed)
             nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
             ctx.next_first_norm = getattr(nxt, "first_norm", lambda: None)() if nxt is not None else None
+            ctx.block_ahead = nxt
             self.blocks[run.layer].forward(residual, ctx, slots)
-        ctx.next_first_norm = ctx.prenormed = None
+        ctx.next_first_norm = ctx.prenormed = ctx.block_ahead = None
+        if streams is not None:
+            # the streams are added up (a read with weights of one and no norm); the final norm reads the sum
+            total = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
+            residual = ops.streams_step(residual, read=(self._ones, None, 0.0, total))
         ops.join_beside(ctx.device)   # what parts asked into L2 on the side stream
         if num_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=ctx.device)

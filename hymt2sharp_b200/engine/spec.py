@@ -35,6 +35,9 @@ class ModelSpec:
     # regular expressions of tensor names that checkpoints of this architecture may hold and the model does not read
     ignorable_tensors: list[str] = field(default_factory=list)
     head_copy: str | None = None      # with a tied head: the name under which a checkpoint may store the head once more
+    # None: the residual is one matrix [T, hidden].  n >= 1: it is kept as n streams [n, T, hidden] (parts.block.StreamsBlock),
+    # all equal to the embedding's output at the start and added up in front of the final norm
+    residual_streams: int | None = None
 
     def __post_init__(self):
         if not self.order:

@@ -1220,17 +1220,19 @@ EPILOGUE_RELU_SQUARED = 3
 _group_tiles: dict = {}
 
 
-def moe_route(chosen: torch.Tensor, weight: torch.Tensor, logits: torch.Tensor, correction: torch.Tensor | None) -> None:
-    """From router outputs logits [T, R] (float32): scores = softmax over all R; chosen [T, top] (int32) = the `top` largest of
-    score + correction, best first, ties to the lower index; weight [T, top] (float32) = their scores, as they are."""
+def moe_route(chosen: torch.Tensor, weight: torch.Tensor, logits: torch.Tensor, correction: torch.Tensor | None,
+              bias: torch.Tensor | None = None, renormalise: bool = False) -> None:
+    """From router outputs logits [T, R] (float32), plus `bias` [R] where one is given: scores = softmax over all R; chosen [T, top]
+    (int32) = the `top` largest of score + correction, best first, ties to the lower index; weight [T, top] (float32) = their
+    scores, as they are, or (`renormalise`) divided by their sum: the softmax over the chosen outputs alone."""
     _need(logits, "logits", torch.float32, 2); _need(chosen, "chosen", torch.int32, 2); _need(weight, "weight", torch.float32, 2)
     T, R = logits.shape
     top = chosen.shape[1]
     if chosen.shape[0] != T or weight.shape != chosen.shape or not (0 < top <= R):
         raise KernelError(f"moe_route: shapes logits {tuple(logits.shape)} chosen {tuple(chosen.shape)} weight {tuple(weight.shape)}")
-    _f32(correction, "correction", R)
-    _check(_lib().hymt2_moe_route(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(correction), c_int(T), c_int(R), c_int(top), _stream()),
-           "moe_route")
+    _f32(correction, "correction", R); _f32(bias, "bias", R)
+    _check(_lib().hymt2_moe_route(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(correction), _ptr(bias), c_int(1 if renormalise else 0),
+                                  c_int(T), c_int(R), c_int(top), _stream()), "moe_route")
 
 
 def moe_tiles(tokens: int, top: int, experts: int, tile: int) -> int:
@@ -1374,7 +1376,8 @@ MOE_SMALL_PAIRS = 64   # up to this many (token, choice) pairs one block routes 
 
 
 def moe_route_place(chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch.Tensor,
-                    logits: torch.Tensor, correction: torch.Tensor | None, experts: int, tile: int) -> None:
+                    logits: torch.Tensor, correction: torch.Tensor | None, experts: int, tile: int, bias: torch.Tensor | None = None,
+                    renormalise: bool = False) -> None:
     """moe_route and moe_place in one launch, for a step of at most MOE_SMALL_PAIRS (token, choice) pairs."""
     _need(logits, "logits", torch.float32, 2); _need(chosen, "chosen", torch.int32, 2); _need(weight, "weight", torch.float32, 2)
     for t, n in ((pair_row, "pair_row"), (row_token, "row_token"), (tile_group, "tile_group")):
@@ -1384,10 +1387,10 @@ def moe_route_place(chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.
     if chosen.shape[0] != T or weight.shape != chosen.shape or pair_row.shape != chosen.shape or not (0 < top <= R) or T * top > MOE_SMALL_PAIRS \
             or row_token.numel() < tiles * tile or tiles < moe_tiles(T, top, experts, tile):
         raise KernelError("moe_route_place: shapes do not fit, or a buffer is too small")
-    _f32(correction, "correction", R)
+    _f32(correction, "correction", R); _f32(bias, "bias", R)
     _check(_lib().hymt2_moe_route_place_small(_ptr(chosen), _ptr(weight), _ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(logits),
-                                              _ptr(correction), c_int(T), c_int(R), c_int(top), c_int(experts), c_int(tile), c_int(tiles),
-                                              _stream()), "moe_route_place")
+                                              _ptr(correction), _ptr(bias), c_int(1 if renormalise else 0), c_int(T), c_int(R), c_int(top),
+                                              c_int(experts), c_int(tile), c_int(tiles), _stream()), "moe_route_place")
 
 
 MOE_COMBINE_NORM_MAX_WIDTH = 12000   # a row of the fused combine-and-norm kernel lies in shared memory
@@ -1415,3 +1418,159 @@ def moe_combine_norm(residual: torch.Tensor, rows: torch.Tensor | None, branch: 
                                          _ptr(y), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(pair_row), _ptr(weight), _ptr(gain),
                                          c_int(dtype_code(gain.dtype)), c_int(T), c_int(H), c_int(pair_row.shape[1]), c_float(eps), _stream()),
            "moe_combine_norm")
+
+
+# -- a residual kept as several streams --------------------------------------------------------------------------------------------
+MAX_STREAMS, MAX_BRANCHES = 8, 4
+
+
+def streams_fill(X: torch.Tensor) -> None:
+    """X float32 [streams, T, width]: every stream becomes a copy of stream 0."""
+    _need(X, "X", torch.float32, 3)
+    _check(_lib().hymt2_streams_fill(_ptr(X), c_int(X.shape[0]), c_int(X.shape[1]), c_int(X.shape[2]), _stream()), "streams_fill",
+           1 if X.shape[0] > 1 else 0)
+
+
+def streams_step(X: torch.Tensor, write: tuple | None = None, read: tuple | None = None) -> torch.Tensor | None:
+    """One pass over the streams X float32 [streams, T, width], a block per token.
+    write = (mix [streams, streams] indexed [from, to], w_out [streams], branches [float32 [T, width], ...], scales [float, ...]):
+        y = sum_b scales[b] * branches[b];  X'[r] = sum_s mix[s, r] X[s] + w_out[r] * y, every stream from the old ones.
+    read = (w_in [streams], gain [width] or None, eps, out): u = sum_s w_in[s] X[s] of the streams as the write left them;
+        out = u / sqrt(mean(u^2) + eps) * gain, or u itself (float32) without a gain.  Returns out."""
+    _need(X, "X", torch.float32, 3)
+    S, T, W = X.shape
+    mix = w_out = w_in = gain = out = None
+    eps, branches, scales = 0.0, [], []
+    if write is not None:
+        mix, w_out, branches, scales = write
+        _f32(mix, "mix", S * S); _f32(w_out, "w_out", S)
+        if not (0 < len(branches) <= MAX_BRANCHES) or len(scales) != len(branches):
+            raise KernelError(f"streams_step: {len(branches)} branches (1 to {MAX_BRANCHES})")
+        for b in branches:
+            _need(b, "branch", torch.float32, 2)
+            if b.shape != (T, W):
+                raise KernelError(f"streams_step: a branch is {tuple(b.shape)}, the streams hold rows of {(T, W)}")
+    if read is not None:
+        w_in, gain, eps, out = read
+        _f32(w_in, "w_in", S); _need(out, "out", None, 2)
+        if out.shape != (T, W) or (gain is None and out.dtype != torch.float32):
+            raise KernelError(f"streams_step: out is {tuple(out.shape)} {out.dtype}")
+        if gain is not None:
+            _need(gain, "gain", None, 1)
+            if gain.shape[0] != W:
+                raise KernelError("streams_step: the gain's width differs")
+    if S > MAX_STREAMS or (write is None and read is None):
+        raise KernelError(f"streams_step: {S} streams (at most {MAX_STREAMS}), and something to do")
+    ptrs = (c_void_p * max(1, len(branches)))(*[b.data_ptr() for b in branches])
+    sc = (c_float * max(1, len(scales)))(*[float(v) for v in scales])
+    _check(_lib().hymt2_streams_step(_ptr(X), c_int(S), c_int(T), c_int(W), _ptr(mix), _ptr(w_out), ptrs, sc, c_int(len(branches)),
+                                     _ptr(w_in), _ptr(gain), c_int(dtype_code(gain.dtype) if gain is not None else F32), c_float(eps),
+                                     _ptr(out), c_int(dtype_code(out.dtype) if out is not None else F32), _stream()), "streams_step")
+    return out
+
+
+# -- mixers with a matrix of state per head ------------------------------------------------------------------------------------------
+SCAN_FIXED_DECAY, SCAN_TOKEN_DECAY = 0, 1
+
+
+def linear_scan_chunking() -> tuple[int, int]:
+    """(tokens of a chunk, the longest portion's length from which a step runs in three passes over chunks)."""
+    return int(_lib().hymt2_linear_scan_chunk()), int(_lib().hymt2_linear_scan_min_chunked())
+
+
+def linear_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mode: int, state: torch.Tensor, state_offset: int,
+                cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int, heads: int, dk: int, dv: int,
+                decay: torch.Tensor | None = None, k_scale: float = 1.0, x: torch.Tensor | None = None, w0: torch.Tensor | None = None,
+                u: torch.Tensor | None = None, chunks: tuple | None = None) -> None:
+    """The recurrence over a matrix of state S [dk, dv] float32 per (sequence, head), which lies at byte `state_offset` of the
+    sequence's state row as [heads, dk, dv] and is ignored by a sequence that starts at position 0.
+    SCAN_FIXED_DECAY: S = decay[h] S + (k_scale k_t) v_t^T; out_t = S^T q_t.
+    SCAN_TOKEN_DECAY: out_t = (S + diag(u[h]) k_t v_t^T)^T q_t; S = diag(w_t) S + k_t v_t^T with w_t = exp(-exp(x_t + w0)).
+    q, k [T, heads * dk] and v [T, heads * dv] in the compute type (rows may be columns of wider matrices); x [T, heads * dk] float32;
+    out [T, heads * dv] float32.  `chunks` = (count, chunk_seq, chunk_first, chunk_len, seq_chunk0) int32 on the device: the
+    three-pass form over those chunks; None: one serial walk per sequence."""
+    _need(out, "out", torch.float32, 2)
+    T = out.shape[0]
+    ldq, ldk, ldv = _rows_view(q, "q"), _rows_view(k, "k", q.dtype), _rows_view(v, "v", q.dtype)
+    if q.shape != (T, heads * dk) or k.shape != q.shape or v.shape != (T, heads * dv) or out.shape[1] != heads * dv:
+        raise KernelError(f"linear_scan: shapes q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)} out {tuple(out.shape)}")
+    ldx = 0
+    if mode == SCAN_FIXED_DECAY:
+        _f32(decay, "decay", heads)
+    else:
+        ldx = _rows_view(x, "x", torch.float32)
+        _f32(w0, "w0", heads * dk); _f32(u, "u", heads * dk)
+        if x.shape != (T, heads * dk):
+            raise KernelError(f"linear_scan: x is {tuple(x.shape)}")
+    if state.dtype != torch.uint8 or state.dim() != 2 or state_offset % 4 or state_offset + 4 * heads * dk * dv > state.shape[1]:
+        raise KernelError("linear_scan: the state rows are too short")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    count, B, A, cs, cf, cl, sc0, launches_ = 0, None, None, None, None, None, None, 1
+    if chunks is not None:
+        count, cs, cf, cl, sc0 = chunks
+        B = torch.empty(count * heads * dk * dv, dtype=torch.float32, device=out.device)
+        A = torch.empty(count * heads * dk, dtype=torch.float32, device=out.device) if mode == SCAN_TOKEN_DECAY else None
+        launches_ = 3
+    _check(_lib().hymt2_linear_scan(_ptr(out), _ptr(q), _ptr(k), _ptr(v), c_int(dtype_code(q.dtype)), c_long(ldq), c_long(ldk), c_long(ldv),
+                                    _ptr(x), c_long(ldx), _ptr(w0), _ptr(u), _ptr(decay), c_float(k_scale), c_int(mode), _ptr(state),
+                                    c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens),
+                                    c_int(batch), c_int(heads), c_int(dk), c_int(dv), c_int(count), _ptr(B), _ptr(A), _ptr(cs), _ptr(cf),
+                                    _ptr(cl), _ptr(sc0), _stream()), "linear_scan", launches_)
+
+
+def head_norm_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor | None, heads: int, dv: int,
+                   eps: float) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight[h, :] * silu(gate[t, h, :]); weight and gate are optional,
+    o is float32, gate (rows may be columns of a wider matrix) and out have the compute type."""
+    _need(out, "out", None, 2); _need(o, "o", torch.float32, 2)
+    T = out.shape[0]
+    ldg = 0
+    if gate is not None:
+        ldg = _rows_view(gate, "gate", out.dtype)
+        if gate.shape != out.shape:
+            raise KernelError("head_norm_gate: the gate's shape differs")
+    _f32(weight, "weight", heads * dv)
+    if out.shape != (T, heads * dv) or o.shape != out.shape:
+        raise KernelError(f"head_norm_gate: shapes out {tuple(out.shape)} o {tuple(o.shape)}")
+    _check(_lib().hymt2_head_norm_gate(_ptr(out), _ptr(o), _ptr(gate), c_long(ldg), c_int(dtype_code(out.dtype)), _ptr(weight), c_int(T),
+                                       c_int(heads), c_int(dv), c_float(eps), _stream()), "head_norm_gate")
+
+
+def token_shift(mixes: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_offset: int, token_seq: torch.Tensor,
+                cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor) -> None:
+    """mixes[t, s * W : (s + 1) * W] = h[t] + (h[t - 1] - h[t]) * mu[s] for every row s of mu [count, W] (float32).  The row before
+    a sequence's first new token is the float32 [W] at byte `state_offset` of its state row (zeros at position 0), which
+    receives the step's last row."""
+    ldh = _rows_view(h, "h")
+    _need(mixes, "mixes", h.dtype, 2); _need(mu, "mu", torch.float32, 2)
+    T, W = h.shape
+    count = mu.shape[0]
+    if mixes.shape != (T, count * W) or mu.shape[1] != W:
+        raise KernelError(f"token_shift: shapes mixes {tuple(mixes.shape)} h {tuple(h.shape)} mu {tuple(mu.shape)}")
+    if state.dtype != torch.uint8 or state.dim() != 2 or state_offset % 4 or state_offset + 4 * W > state.shape[1]:
+        raise KernelError("token_shift: the state rows are too short")
+    for t, n in ((token_seq, "token_seq"), (cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_token_shift(_ptr(mixes), _ptr(h), c_long(ldh), c_int(dtype_code(h.dtype)), _ptr(mu), c_int(count), _ptr(state),
+                                    c_long(state_offset), c_long(state.stride(0)), _ptr(token_seq), _ptr(cu_seqlens), _ptr(slot_ids),
+                                    _ptr(kv_lens), c_int(T), c_int(W), _stream()), "token_shift")
+
+
+GATED_SILU, GATED_GELU_TANH = 0, 1
+
+
+def gated_act(out: torch.Tensor, gate_up: torch.Tensor, kind: int) -> None:
+    """out[r, c] = act(gate_up[r, c]) * gate_up[r, width + c]; act: GATED_SILU or GATED_GELU_TANH."""
+    _need(out, "out", None, 2); _need(gate_up, "gate_up", out.dtype, 2)
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width):
+        raise KernelError(f"gated_act: shapes out {tuple(out.shape)} gate_up {tuple(gate_up.shape)}")
+    _check(_lib().hymt2_gated_act(_ptr(out), _ptr(gate_up), c_int(dtype_code(out.dtype)), c_int(rows), c_int(width), c_int(kind),
+                                  _stream()), "gated_act")
+
+
+def tanh_(x: torch.Tensor) -> None:
+    """In place on float32 values."""
+    _need(x, "x", torch.float32)
+    _check(_lib().hymt2_tanh(_ptr(x), c_long(x.numel()), _stream()), "tanh")

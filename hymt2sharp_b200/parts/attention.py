@@ -11,7 +11,10 @@ Beyond that form, chosen by parameters: values of another width than keys (`valu
 (`scale`); the q/k norm BEFORE the rotation (`norm_first`), per head with one gain of head_dim entries (`qk_norm` True or
 "head") or over a token's whole q (and k) projection with a gain as wide as the projection ("all"); a sink in the softmax
 (`sink`: one more term in the denominator, of score 0 and without a value); and a layer without key/value projections of its
-own (`own_kv` False), which reads the cache plane of the run that the model's order names for it, with its own queries.
+own (`own_kv` False), which reads the cache plane of the run that the model's order names for it, with its own queries;
+biases of the q, k and v projections (`q_bias`, `k_bias`, `v_bias`: stored vectors, added before the rotation); and a gate
+per head (`head_gate`: a stored matrix [heads, hidden]; head h's output is multiplied by sigmoid((W_gate x)_h) in front of
+the output projection).
 The classic form (none of these) runs the fused and tensor-core kernels; the others run the general kernels, and the
 tensor-core attention where it takes the shape.
 """
@@ -39,7 +42,8 @@ class GQAAttention:
                  position: PartSpec | None, q_proj: str, k_proj: str | None, v_proj: str | None, o_proj: str,
                  q_norm: str | None = None, k_norm: str | None = None, window: int | None = None,
                  value_dim: int | None = None, scale: float | None = None, norm_first: bool = False, sink: bool = False,
-                 own_kv: bool = True):
+                 own_kv: bool = True, q_bias: str | None = None, k_bias: str | None = None, v_bias: str | None = None,
+                 head_gate: str | None = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} kv heads")
         if qk_norm not in (False, True, None, "head", "all"):
@@ -54,11 +58,15 @@ class GQAAttention:
         if self.own_kv and (k_proj is None or v_proj is None):
             raise ValueError("an attention with keys and values of its own needs the names of their projections")
         # the form that the fused projection and the classic kernels know
+        biased = q_bias is not None or k_bias is not None or v_bias is not None
+        if biased and (q_bias is None or (self.own_kv and (k_bias is None or v_bias is None))):
+            raise ValueError("biases come for every projection that the attention has, or for none")
         self.classic = (self.value_dim == head_dim and not self.norm_first and not self.sink and self.own_kv
-                        and self.qk_norm != "all")
+                        and self.qk_norm != "all" and not biased and head_gate is None)
         if self.classic and (head_dim % 8 or head_dim > 256):   # what the classic kernels take; the tensor-core kernels take 64 and 128
             raise ValueError(f"head_dim {head_dim} must be a multiple of 8, at most 256")
-        self.names = dict(q=q_proj, k=k_proj, v=v_proj, o=o_proj, qn=q_norm, kn=k_norm)
+        self.names = dict(q=q_proj, k=k_proj, v=v_proj, o=o_proj, qn=q_norm, kn=k_norm, qb=q_bias, kb=k_bias, vb=v_bias, g=head_gate)
+        self.bias = self.gate = None
         self.position = build_part("position", position) if position is not None else None
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)  # src/HyMT2Sharp/HunyuanDenseModel.Prefill.cs:64
         self.qkv = self.out = self.out_store = self.q_gain = self.k_gain = None
@@ -75,6 +83,13 @@ class GQAAttention:
             t[n["qn"]] = TensorSpec((qd if wide else self.head_dim,), init="gain")
             if self.own_kv:
                 t[n["kn"]] = TensorSpec((kd if wide else self.head_dim,), init="gain")
+        if n["qb"] is not None:
+            t[n["qb"]] = TensorSpec((qd,))
+            if self.own_kv:
+                t[n["kb"]] = TensorSpec((kd,))
+                t[n["vb"]] = TensorSpec((self.kv_heads * self.value_dim,))
+        if n["g"] is not None:
+            t[n["g"]] = TensorSpec((self.heads, h))
         if self.position is not None:
             t.update(self.position.tensors())
         return t
@@ -93,6 +108,11 @@ class GQAAttention:
         self.qkv = Linear(compute_form(torch.cat(rows, dim=0), device, dtype), role="qkv" if self.own_kv else "q_proj")
         self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
         self.out_store = Linear(self.out.weight, ops.EPILOGUE_STORE, role="o_proj")
+        if n["qb"] is not None:
+            self.bias = torch.cat([weights[name].to(device).float().reshape(-1)
+                                   for name in ([n["qb"]] + ([n["kb"], n["vb"]] if self.own_kv else []))]).contiguous()
+        if n["g"] is not None:
+            self.gate = Linear(compute_form(weights[n["g"]], device, dtype), role="head_gate")
         if self.qk_norm:
             self.q_gain = compute_form(weights[n["qn"]], device, dtype)
             self.k_gain = compute_form(weights[n["kn"]], device, dtype) if self.own_kv else None
@@ -155,6 +175,9 @@ class GQAAttention:
         k_plane, v_plane = ctx.cache.plane(slot.group, slot.plane)
         block_table = ctx.cache.tables[slot.group]
         proj = self.qkv(x, ctx=ctx)
+        if self.bias is not None:
+            ops.bias_act(proj, self.bias, 0)
+        gate = self.gate(x, ctx=ctx) if self.gate is not None else None     # [T, heads], read behind the attention
         q = torch.empty((T, nh * d), dtype=proj.dtype, device=proj.device)
         mode = ops.NORM_NONE if not self.qk_norm else (ops.NORM_ALL_BEFORE if self.qk_norm == "all" else
                                                        (ops.NORM_HEAD_BEFORE if self.norm_first else ops.NORM_HEAD_AFTER))
@@ -172,6 +195,8 @@ class GQAAttention:
                 ml = torch.empty(nm, dtype=torch.float32, device=out.device)
             ops.attention_simt_kv(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
                                   ctx.max_new_tokens, nh, nkv, d, dv, self.scale, self.window, self.sink, split, max_splits, acc, ml)
+        if gate is not None:
+            ops.sigmoid_gate(out, gate, nh, dv, True)
         if store:
             self.out_store(out, out=residual)
         else:

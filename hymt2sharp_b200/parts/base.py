@@ -163,6 +163,8 @@ class StepContext:
     norm_ahead: object = None
     next_first_norm: object = None
     prenormed: object = None
+    # the block that runs next (None behind the last one), for a block whose last kernel can prepare that block's input
+    block_ahead: object = None
 
     @property
     def decode(self) -> bool:

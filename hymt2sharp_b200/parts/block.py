@@ -189,3 +189,127 @@ class SandwichBlock:
 
 
 register_part("block", "sandwich", SandwichBlock)
+
+
+class StreamsBlock:
+    """A pre-norm block over a residual that is kept as several streams (hyper-connections), with any number of mixers side
+    by side.  X is float32 [streams, T, hidden]; for sublayer q (1: the mixers, 2: the feed-forward) with the stored vectors
+    in_q, out_q [streams] and the matrix mix_q [streams, streams], indexed [from, to]:
+
+        u = sum_s in_q[s] X[s];   y = sublayer(norm_q(u));   X[r] <- sum_s mix_q[s, r] X[s] + out_q[r] * y   (every r from the old X)
+
+    The first sublayer's y is sum_i scale_i * mixer_i(norm_1(u)): the mixers read the same rows, each has its own cache
+    plane or state (cache_needs() / state_bytes() list them in order) and writes a float32 buffer of its own; the scales
+    are applied in float32 where the buffers are added.  `hyper1` / `hyper2` None: one stream without stored tables, which is
+    the plain residual sum X <- X + y.  The write of a sublayer and the read and norm of the next one (this block's
+    feed-forward, or the first sublayer of the block that runs next, `ctx.block_ahead`) are one kernel; the rows that such
+    a kernel prepared wait in `ctx.shared["stream_rows"]`."""
+
+    def __init__(self, streams: int, norm1: PartSpec, mixers: list, norm2: PartSpec | None = None,
+                 feed_forward: PartSpec | None = None, hyper1: dict | None = None, hyper2: dict | None = None):
+        """`mixers`: [(PartSpec, scale), ...]; `hyper1` / `hyper2`: {"in": name, "out": name, "mix": name} of the stored tables."""
+        if not mixers or len(mixers) > ops.MAX_BRANCHES:
+            raise ValueError(f"a block holds 1 to {ops.MAX_BRANCHES} mixers side by side, got {len(mixers)}")
+        if not (1 <= streams <= ops.MAX_STREAMS):
+            raise ValueError(f"{streams} streams (1 to {ops.MAX_STREAMS})")
+        if (hyper1 is None or (feed_forward is not None and hyper2 is None)) and streams != 1:
+            raise ValueError("several streams need the tables that mix them")
+        self.streams = int(streams)
+        self.norm1 = build_part("norm", norm1)
+        self.mixers = [build_part("mixer", m) for m, _ in mixers]
+        self.scales = [float(s) for _, s in mixers]
+        self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
+        self.norm2 = build_part("norm", norm2) if feed_forward is not None else None
+        self.names = [hyper1, hyper2 if feed_forward is not None else None]
+        self.tables = [None, None]     # per sublayer: (w_in, w_out, mix) float32 on the device
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, *self.mixers, self.norm2, self.feed_forward) if p is not None)
+
+    def cache_needs(self) -> list:
+        return [m.cache_need() for m in self.mixers]
+
+    def state_bytes(self) -> list:
+        return [int(m.state_bytes()) for m in self.mixers]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts())
+
+    def tensors(self):
+        from ..weights.loader import TensorSpec
+        t, S = {}, self.streams
+        for p in self.parts():
+            t.update(p.tensors())
+        for names in self.names:
+            if names is not None:
+                t[names["in"]] = TensorSpec((S,), init="gain")
+                t[names["out"]] = TensorSpec((S,), init="gain")
+                t[names["mix"]] = TensorSpec((S, S), init="identity")
+        return t
+
+    def load(self, weights, device, dtype):
+        import torch
+        for p in self.parts():
+            p.load(weights, device, dtype)
+        for q, names in enumerate(self.names):
+            if names is not None:
+                self.tables[q] = tuple(weights[names[k]].to(device).float().reshape(-1).contiguous() for k in ("in", "out", "mix"))
+            else:
+                self.tables[q] = tuple(torch.ones(1, dtype=torch.float32, device=device) for _ in range(3))
+
+    def first_norm(self):
+        return None   # (the products of the block in front cannot prepare this block's input: it is a mixture of streams)
+
+    def first_read(self):
+        """What the block in front needs to prepare this block's first input: (w_in, norm)."""
+        return self.tables[0][0], self.norm1
+
+    def _read(self, X, w_in, norm, ctx):
+        import torch
+        out = torch.empty(X.shape[1:], dtype=ctx.dtype, device=X.device)
+        return ops.streams_step(X, read=(w_in, norm.gain, norm.eps, out))
+
+    def _write(self, X, q: int, branches, scales, ctx, ahead):
+        """Sublayer q's outputs go into the streams; `ahead` = (w_in, norm) of the read that follows (or None)."""
+        import torch
+        _, w_out, mix = self.tables[q]
+        if ahead is None:
+            ops.streams_step(X, write=(mix, w_out, branches, scales))
+            return None
+        w_in, norm = ahead
+        out = torch.empty(X.shape[1:], dtype=ctx.dtype, device=X.device)
+        return ops.streams_step(X, write=(mix, w_out, branches, scales), read=(w_in, norm.gain, norm.eps, out))
+
+    def forward(self, residual, ctx, slots) -> None:
+        import torch
+        X = residual
+        if X.dim() != 3 or X.shape[0] != self.streams:
+            raise ValueError(f"this block reads {self.streams} residual streams [streams, T, hidden], got {tuple(X.shape)}")
+        ctx.weights_ahead = ctx.norm_ahead = ctx.prenormed = None
+        left = ctx.shared.pop("stream_rows", None)
+        if left is not None and left[0] is X and left[1] is self:
+            h = left[2]
+        else:
+            h = self._read(X, self.tables[0][0], self.norm1, ctx)
+        branches = []
+        for mixer, slot in zip(self.mixers, slots):
+            y = torch.empty(X.shape[1:], dtype=torch.float32, device=X.device)
+            mixer.forward(h, y, ctx, slot, store=True)
+            branches.append(y)
+        ctx.prenormed = None
+        nxt = getattr(ctx, "block_ahead", None)
+        after = nxt.first_read() if nxt is not None and hasattr(nxt, "first_read") and getattr(nxt, "streams", None) == self.streams else None
+        if self.feed_forward is None:
+            rows = self._write(X, 0, branches, self.scales, ctx, after)
+        else:
+            h = self._write(X, 0, branches, self.scales, ctx, (self.tables[1][0], self.norm2))
+            y = branches[0]
+            self.feed_forward.forward(h, y, ctx, store=True)
+            ctx.prenormed = None
+            rows = self._write(X, 1, [y], [1.0], ctx, after)
+        if rows is not None:
+            ctx.shared["stream_rows"] = (X, nxt, rows)
+
+
+register_part("block", "streams", StreamsBlock)

@@ -1,7 +1,9 @@
 """RMSNorm part: y = x / sqrt(mean(x^2) + eps) * gain
 (src/HyMT2Sharp/Ops.cs:29-89).  With `groups` > 1 a row is cut into that many equal
 consecutive parts and each part is divided by its own root mean square; the gain
-spans the whole row."""
+spans the whole row.  With `offset` the stored weight w lies around zero and the gain
+is offset + w, added in float32 and kept so (a gain of 1 + w rounded to bfloat16 would
+lose most of w)."""
 from __future__ import annotations
 
 import torch
@@ -15,8 +17,9 @@ from .linear import compute_form
 class RMSNorm:
     graph_safe = True  # its forward only launches kernels on the current stream
 
-    def __init__(self, dim: int, eps: float, weight: str, groups: int = 1):
+    def __init__(self, dim: int, eps: float, weight: str, groups: int = 1, offset: float = 0.0):
         self.dim, self.eps, self.weight_name, self.groups = int(dim), float(eps), weight, int(groups)
+        self.offset = float(offset)
         if self.groups < 1 or self.dim % self.groups:
             raise ValueError(f"a norm over {dim} entries cannot be cut into {groups} equal parts")
         # y = x * r * gain with ONE row scale r: the products around it can take it over (parts.base.Prenormed);
@@ -25,10 +28,13 @@ class RMSNorm:
         self.gain = None
 
     def tensors(self):
-        return {self.weight_name: TensorSpec((self.dim,), init="gain")}
+        return {self.weight_name: TensorSpec((self.dim,), init="normal" if self.offset else "gain")}
 
     def load(self, weights, device, dtype):
-        self.gain = compute_form(weights[self.weight_name], device, dtype)
+        if self.offset:
+            self.gain = (weights[self.weight_name].to(device).float() + self.offset).contiguous()
+        else:
+            self.gain = compute_form(weights[self.weight_name], device, dtype)
 
     def forward(self, x: torch.Tensor, ctx, out_dtype: torch.dtype, rows_index: torch.Tensor | None = None,
                 rows: int | None = None, scale: float = 1.0, fresh: bool = False):

@@ -29,10 +29,10 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 
 @dataclass(frozen=True)
 class TensorSpec:
-    shape: tuple
+    shape: tuple         # an entry of -1 stands for any size: the checkpoint's own (a width that no configuration key gives)
     kind: str = "float"  # "float" or "int"
     optional: bool = False
-    init: str = "normal"  # random-weights rule: "normal" = N(0, sigma), "gain" = 1 + N(0, sigma)
+    init: str = "normal"  # random-weights rule: "normal" = N(0, sigma), "gain" = 1 + N(0, sigma), "identity" = I + N(0, sigma)
     same_as: str | None = None  # an optional tensor that, when present, must equal this other tensor; it is not loaded
 
 
@@ -113,7 +113,7 @@ def load_checkpoint(folder: str, expected: dict[str, TensorSpec], ignorable=()) 
         if name not in owners:
             continue
         e = owners[name].entries[name]
-        if tuple(e["shape"]) != tuple(spec.shape):
+        if len(e["shape"]) != len(spec.shape) or any(w != -1 and w != g for w, g in zip(spec.shape, e["shape"])):
             wrong_shape.append((name, tuple(spec.shape), tuple(e["shape"])))
         is_float = e["dtype"] in ("BF16", "F16", "F32", "F64")
         if (spec.kind == "float") != is_float or e["dtype"] == "BOOL":

@@ -1,7 +1,7 @@
 """Random-weights mode: writes a model folder (config.json, model.safetensors)
 from a configuration and a seed.
 
-Matrices and embeddings are N(0, sigma); norm gains are 1 + N(0, sigma).  The
+Matrices and embeddings are N(0, sigma); norm gains are 1 + N(0, sigma); a matrix marked "identity" is I + N(0, sigma).  The
 values are drawn tensor by tensor, in the order of the architecture's tensor
 list, from one torch CPU generator seeded with `seed`, in float32, then stored
 as bfloat16 (norm gains as float32 when `gain_dtype` says so).
@@ -30,6 +30,8 @@ def write_random_model(folder: str, config, seed: int, sigma: float = 0.02,
             continue
         if spec.kind != "float":
             raise ValueError(f"random weights: no rule for the integer tensor '{name}'")
+        if any(n < 0 for n in spec.shape):
+            raise ValueError(f"random weights: the configuration leaves a size of '{name}' {list(spec.shape)} open")
         is_gain = spec.init == "gain"
         out = torch.empty(spec.shape, dtype=gain_dtype if is_gain else torch.bfloat16)
         rows = spec.shape[0]
@@ -39,6 +41,8 @@ def write_random_model(folder: str, config, seed: int, sigma: float = 0.02,
             x = torch.randn((r1 - r0, flat.shape[1]), generator=gen, dtype=torch.float32) * sigma
             if is_gain:
                 x += 1.0
+            elif spec.init == "identity":
+                x += torch.eye(rows, flat.shape[1])[r0:r1]
             flat[r0:r1] = x.to(out.dtype)
         tensors[name] = out
     os.makedirs(folder, exist_ok=True)
