@@ -94,7 +94,8 @@ def gated_window_mixer(h: torch.Tensor, w: dict, p: str, m: dict, positions: tor
     v = (h @ w[p + "v"].T + w[p + "v.b"]).view(T, G, dv)
     rot = m.get("rot") or {"dims": 0, "base": 1.0}
     q, k = rotate(q, positions, rot["dims"], rot["base"]), rotate(k, positions, rot["dims"], rot["base"])
-    o = window_attention(q, k, v, m["scale"], m["mask"]["size"])
+    window = m["mask"]["size"] if m.get("mask") else T       # without a mask: every token before
+    o = window_attention(q, k, v, m["scale"], window)
     gate = torch.sigmoid(h @ w[p + "g"].T)                      # [T, H]
     return (o * gate[:, :, None]).reshape(T, H * dv) @ w[p + "o"].T
 
