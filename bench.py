@@ -140,7 +140,7 @@ def reference_arm() -> int:
     return 0
 
 
-# ---- another design beside the flagship: `--design pemezen`, `--design novunex` ------------------------------------------------
+# ---- another design beside the flagship: `--design pemezen`, `--design novunex`, `--design rutetar` ----------------------------
 # Sizes that resemble a real model's layers (random weights), and a Hunyuan-dense model of the same width, depth and
 # nearly the same number of weights per layer beside it: the closest model that the library has.
 DESIGN_SIZES = {
@@ -180,11 +180,48 @@ def novunex_config(size: str, layers: int):
     return NovunexConfig.from_dict(dict(architecture="Novunex", vocab=z["vocab"], width=z["width"], layers=entries, norm=dict(eps=1e-6)))
 
 
+# Rutetar: of every four layers three are retention (heads of 128 keys and 128 values) and the third runs attention in a
+# sliding window (with a gate per head) and time mixing (heads of 64) side by side; the feed-forward alternates between dense
+# (tanh-GELU gate) and a mixture of `experts` experts of width `ff`, `top` chosen; the residual is kept as two streams
+RUTETAR_SIZES = {
+    "s": dict(width=1024, vocab=32768, ret_heads=8, ret_dim=128, ret_vdim=128, heads=8, kv_heads=2, dim=128, vdim=128, window=1024,
+              rot_dims=64, mix_heads=16, mix_dim=64, mix_rank=64, dense_ff=2816, experts=16, top=4, ff=512, streams=2,
+              dense=DESIGN_SIZES["s"]["dense"]),
+    "m": dict(width=2048, vocab=65536, ret_heads=16, ret_dim=128, ret_vdim=128, heads=16, kv_heads=4, dim=128, vdim=128, window=2048,
+              rot_dims=64, mix_heads=32, mix_dim=64, mix_rank=64, dense_ff=5632, experts=32, top=4, ff=1024, streams=2,
+              dense=DESIGN_SIZES["m"]["dense"]),
+}
+RUTETAR_ORDER = ["retention dense", "retention moe", "parallel dense", "retention moe"]   # repeated up to --layers
+
+
+def rutetar_config(size: str, layers: int):
+    from hymt2sharp_b200.config import RutetarConfig
+    z = RUTETAR_SIZES[size]
+    entries = []
+    for i in range(layers):
+        kind, ff = RUTETAR_ORDER[i % len(RUTETAR_ORDER)].split()
+        if kind == "retention":
+            decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, z["ret_heads"] - 1)) for h in range(z["ret_heads"])]
+            mixer = dict(heads=z["ret_heads"], dim=z["ret_dim"], vdim=z["ret_vdim"], decay=decay)
+        else:
+            left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5,
+                        mask=dict(size=z["window"]), rot=dict(dims=z["rot_dims"], base=1000000.0))
+            mixer = dict(left=left, right=dict(heads=z["mix_heads"], dim=z["mix_dim"], rank=z["mix_rank"]), left_scale=0.7, right_scale=0.7)
+        mlp = dict(kind="dense", ff=z["dense_ff"]) if ff == "dense" else \
+            dict(kind="moe", expert=dict(ff=z["ff"]), router=dict(experts=z["experts"], top=z["top"]))
+        entries.append(dict(type=kind, mixer=mixer, mlp=mlp))
+    return RutetarConfig.from_dict(dict(architecture="Rutetar", vocab=z["vocab"], width=z["width"], layers=entries, norm=dict(eps=1e-6),
+                                        streams=z["streams"]))
+
+
+DESIGN_TABLES = {"pemezen": DESIGN_SIZES, "novunex": NOVUNEX_SIZES, "rutetar": RUTETAR_SIZES}
+
+
 def make_design_models(size: str, layers: int, design: str = "pemezen") -> dict:
     """Model folders with random weights: {the design: ..., "hunyuan_dense": ...}."""
     from hymt2sharp_b200.config import HunyuanDenseConfig, PemezenConfig
     from hymt2sharp_b200.weights import write_random_model
-    z = (NOVUNEX_SIZES if design == "novunex" else DESIGN_SIZES)[size]
+    z = DESIGN_TABLES[design][size]
     rot = dict(dims=z.get("rot_dim"), base=10000.0, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
     entries = []
     for i in range(layers if design == "pemezen" else 0):
@@ -197,6 +234,8 @@ def make_design_models(size: str, layers: int, design: str = "pemezen") -> dict:
         entries.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=z["ff"])))
     if design == "novunex":
         new = novunex_config(size, layers)
+    elif design == "rutetar":
+        new = rutetar_config(size, layers)
     else:
         new = PemezenConfig.from_dict(dict(architecture="Pemezen", vocab=z["vocab"], width=z["width"], layers=entries,
                                            norm=dict(eps=1e-6, groups=2), canon=dict(taps=4), embedding=dict(scale=1.0), logit_softcap=30.0))
@@ -222,7 +261,7 @@ def design_bench(args) -> int:
     from hymt2sharp_b200.sampling import BatchSampler, GREEDY
 
     pk, pk_source = peaks()
-    z = (NOVUNEX_SIZES if args.design == "novunex" else DESIGN_SIZES)[args.design_size]
+    z = DESIGN_TABLES[args.design][args.design_size]
     layers = args.layers or 8
     batch, context, steps, warmup = args.batch or 8, args.prefill, max(1, args.decode or args.steps or 32), max(3, args.warmup)
     dtype = {"bf16": "bfloat16", "fp32": "float32"}[args.dtype]
@@ -423,7 +462,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-kernels", action="store_true", help="skip the kernels timed alone")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--design", default=None, choices=["pemezen", "novunex"],
+    ap.add_argument("--design", default=None, choices=["pemezen", "novunex", "rutetar"],
                     help="instead of the flagship workload: prefill (--prefill tokens) and decode (--batch sequences of --prefill tokens, "
                          "--steps steps) of this design beside the Hunyuan-dense model of equal size, with per-kernel times")
     ap.add_argument("--design-size", default="s", choices=sorted(DESIGN_SIZES))

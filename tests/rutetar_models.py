@@ -34,7 +34,7 @@ CONFIGS = {
         _retention(3, 6, 10, [0.9, 0.97, 0.995]),
         _retention(1, 12, 4, [0.98], mlp=_dense(13)),
         _parallel(4, 4, 6, 6, 0.5, 90, 6, 300.0, 1, 7, 2, 1.0, 0.5, mlp=_moe(3, 3, 5)),
-    ]), seed=31, sigma=0.15),
+    ]), seed=31, sigma=0.1),
     # sizes in multiples of 16: one stream with its tables; heads of 64 and 128 for keys and values, on which the bfloat16
     # engine takes its tensor-core attention; state columns held in registers (16, 64) ; a loop over the two middle layers;
     # an attention without a window; 12 experts of which 3 are chosen
@@ -53,21 +53,40 @@ CONFIGS = {
 }
 
 ROUTER_SPREAD = 2.0
+# Which experts a token gets is a discontinuous function of the router's input, and a recurrent state carries one token's
+# other expert into every token behind it.  For the bfloat16 engine the models named here get routers whose choice rests on
+# the bias (outputs a unit and a half apart, the input's share a fraction of that): every token takes the same experts with
+# weights of its own, and no choice rests on a rounding.  The 32-bit engine runs the routers that choose token by token.
+STEADY = ("odd",)
+STEADY_GAP, STEADY_SHARE = 1.5, 0.2
+
+
+def variant(name: str, dtype: str) -> str:
+    """The name of the model folder that a test of `name` in `dtype` uses."""
+    return name + "/steady" if dtype == "bfloat16" and name in STEADY else name
 
 
 def make_model_dir(folder: str, name: str) -> str:
     import os
+    import torch
     from safetensors.torch import load_file, save_file
     from hymt2sharp_b200.config import RutetarConfig
     from hymt2sharp_b200.weights import write_random_model
+    name, _, steady = name.partition("/")
     spec = CONFIGS[name]
     write_random_model(folder, RutetarConfig.from_dict(spec["config"]), spec["seed"], spec["sigma"])
     # routers with a wide spread of outputs: a choice between two experts that rests on the last bits would make the
     # comparison of two precisions a comparison of two different sums
     path = os.path.join(folder, "model.safetensors")
     tensors = load_file(path)
-    for k in tensors:
-        if k.endswith(".mlp.router") or k.endswith(".mlp.router.b"):
+    gen = torch.Generator().manual_seed(spec["seed"])
+    for k in sorted(tensors):
+        if steady and k.endswith(".mlp.router"):
+            tensors[k] = (tensors[k].float() * STEADY_SHARE).to(tensors[k].dtype)
+        elif steady and k.endswith(".mlp.router.b"):
+            n = tensors[k].numel()
+            tensors[k] = (torch.randperm(n, generator=gen).float() * STEADY_GAP).to(tensors[k].dtype)
+        elif k.endswith(".mlp.router") or k.endswith(".mlp.router.b"):
             tensors[k] = (tensors[k].float() * ROUTER_SPREAD).to(tensors[k].dtype)
     save_file(tensors, path)
     return folder
