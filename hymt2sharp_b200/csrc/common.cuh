@@ -120,3 +120,24 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
         else if ((code) == HYMT2_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
         else { hymt2_set_error("unknown dtype code %d", (int)(code)); return HYMT2_ERR_ARGUMENT; } \
     } while (0)
+
+// V neighbouring elements in one access of V * sizeof(T) bytes (the caller has checked the alignment).
+template <typename T, int V> struct Pack { T v[V]; };
+template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T* p) {
+    Pack<T, V> r;
+    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
+    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(r.v) = *reinterpret_cast<const uint2*>(p);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; i++) r.v[i] = p[i];
+    }
+    return r;
+}
+template <typename T, int V> __device__ __forceinline__ void store_pack(T* p, const Pack<T, V>& r) {
+    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
+    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(r.v);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; i++) p[i] = r.v[i];
+    }
+}

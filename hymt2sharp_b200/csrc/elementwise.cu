@@ -10,27 +10,6 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// V neighbouring elements in one access of V * sizeof(T) bytes (the caller has checked the alignment).
-template <typename T, int V> struct Pack { T v[V]; };
-template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T* p) {
-    Pack<T, V> r;
-    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
-    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(r.v) = *reinterpret_cast<const uint2*>(p);
-    else {
-#pragma unroll
-        for (int i = 0; i < V; i++) r.v[i] = p[i];
-    }
-    return r;
-}
-template <typename T, int V> __device__ __forceinline__ void store_pack(T* p, const Pack<T, V>& r) {
-    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
-    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(r.v);
-    else {
-#pragma unroll
-        for (int i = 0; i < V; i++) p[i] = r.v[i];
-    }
-}
-
 // x[r, c] <- act(x[r, c] + bias[c]); the first `act_cols` columns get the tanh form of GELU, the others the bias alone.
 // A thread takes V neighbouring columns (cols is a multiple of V).
 template <typename T, int V>

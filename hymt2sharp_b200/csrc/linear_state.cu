@@ -52,57 +52,110 @@ struct ScanParams {
 };
 
 // One thread's walk over `n` tokens for its column j of one head.  MODE 0: fixed decay, 1: token decay.
-// WRITE_OUT: o is written; the state goes from S (in/out).  `vecs` is shared memory for two tokens' vectors.
+// WRITE_OUT: o is written; the state goes from S (in/out).  `vecs` is shared memory for two tokens' vectors, `us` for the
+// bonus (token decay).  With DK > 0 (state in registers) the next token's vectors are loaded into registers in front of the
+// current token's sums and stored to shared memory behind them, so that the loads' latency lies under the arithmetic; the
+// vectors are read back four entries at a time, and o is summed in four partial sums over i mod 4, added as (0 + 1) + (2 + 3).
 template <typename T, int MODE, int DK, bool WRITE_OUT>
 __device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool live, int row0, int n, float* S, int sstride,
-                                     float* vecs, float gh) {
+                                     float* vecs, const float* us, float gh) {
     const int dk = DK > 0 ? DK : p.dk;
     const int nvec = MODE == 0 ? 2 : 3;              // q, k (, w) per token
     const T* q = (const T*)p.q + (size_t)head * dk;
     const T* k = (const T*)p.k + (size_t)head * dk;
     const T* v = (const T*)p.v + (size_t)head * p.dv;
+    const float* xx = MODE == 1 ? p.x + (size_t)head * dk : nullptr;
+    const float* w0 = MODE == 1 ? p.w0 + (size_t)head * dk : nullptr;
     auto stage = [&](int t, float* dst) {
         const size_t r = (size_t)(row0 + t);
         for (int i = threadIdx.x; i < dk; i += blockDim.x) {
             dst[i] = to_float(q[r * p.ldq + i]);
             const float kk = to_float(k[r * p.ldk + i]);
             dst[dk + i] = MODE == 0 ? kk * p.k_scale : kk;
-            if (MODE == 1) dst[2 * dk + i] = expf(-expf(p.x[r * p.ldx + (size_t)head * dk + i] + p.w0[(size_t)head * dk + i]));
+            if (MODE == 1) dst[2 * dk + i] = expf(-expf(xx[r * p.ldx + i] + w0[i]));
         }
     };
-    const float* uu = MODE == 1 ? p.u + (size_t)head * dk : nullptr;
     stage(0, vecs);
     __syncthreads();
+    if (DK > 0) {
+        constexpr int PER = DK > 0 ? (DK + 31) / 32 : 1;   // entries of a vector that one thread fetches (blocks of 32 or more threads)
+        float vnext = live ? to_float(v[(size_t)row0 * p.ldv + j]) : 0.f;
+        for (int t = 0; t < n; t++) {
+            const float* cur = vecs + (size_t)(t & 1) * nvec * dk;
+            float* nxt = vecs + (size_t)((t + 1) & 1) * nvec * dk;
+            const float vj = vnext;
+            const bool more = t + 1 < n;
+            T fq[PER], fk[PER];
+            float fx[PER];
+            if (more) {
+                const size_t r = (size_t)(row0 + t + 1);
+#pragma unroll
+                for (int e = 0; e < PER; e++) {
+                    const int i = threadIdx.x + e * blockDim.x;
+                    if (i < dk) {
+                        fq[e] = q[r * p.ldq + i];
+                        fk[e] = k[r * p.ldk + i];
+                        if (MODE == 1) fx[e] = xx[r * p.ldx + i];
+                    }
+                }
+                if (live) vnext = to_float(v[r * p.ldv + j]);
+            }
+            const float4* cq = reinterpret_cast<const float4*>(cur);
+            const float4* ck = reinterpret_cast<const float4*>(cur + dk);
+            const float4* cw = reinterpret_cast<const float4*>(cur + 2 * dk);
+            const float4* cu = reinterpret_cast<const float4*>(us);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int g = 0; g < (DK > 0 ? DK : 4) / 4; g++) {
+                const float4 q4 = cq[g], k4 = ck[g];
+                float* s = S + 4 * g;
+                if (MODE == 0) {
+                    s[0] = fmaf(gh, s[0], k4.x * vj); a0 = fmaf(s[0], q4.x, a0);
+                    s[1] = fmaf(gh, s[1], k4.y * vj); a1 = fmaf(s[1], q4.y, a1);
+                    s[2] = fmaf(gh, s[2], k4.z * vj); a2 = fmaf(s[2], q4.z, a2);
+                    s[3] = fmaf(gh, s[3], k4.w * vj); a3 = fmaf(s[3], q4.w, a3);
+                } else {
+                    const float4 w4 = cw[g], u4 = cu[g];
+                    const float kx = k4.x * vj, ky = k4.y * vj, kz = k4.z * vj, kw = k4.w * vj;
+                    a0 = fmaf(q4.x, fmaf(u4.x, kx, s[0]), a0); s[0] = fmaf(w4.x, s[0], kx);
+                    a1 = fmaf(q4.y, fmaf(u4.y, ky, s[1]), a1); s[1] = fmaf(w4.y, s[1], ky);
+                    a2 = fmaf(q4.z, fmaf(u4.z, kz, s[2]), a2); s[2] = fmaf(w4.z, s[2], kz);
+                    a3 = fmaf(q4.w, fmaf(u4.w, kw, s[3]), a3); s[3] = fmaf(w4.w, s[3], kw);
+                }
+            }
+            if (more) {
+#pragma unroll
+                for (int e = 0; e < PER; e++) {
+                    const int i = threadIdx.x + e * blockDim.x;
+                    if (i < dk) {
+                        nxt[i] = to_float(fq[e]);
+                        const float kk = to_float(fk[e]);
+                        nxt[dk + i] = MODE == 0 ? kk * p.k_scale : kk;
+                        if (MODE == 1) nxt[2 * dk + i] = expf(-expf(fx[e] + w0[i]));
+                    }
+                }
+            }
+            if (WRITE_OUT && live) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = (a0 + a1) + (a2 + a3);
+            __syncthreads();
+        }
+        return;
+    }
     for (int t = 0; t < n; t++) {
         float* cur = vecs + (size_t)(t & 1) * nvec * dk;
         if (t + 1 < n) stage(t + 1, vecs + (size_t)((t + 1) & 1) * nvec * dk);
         const float vj = live ? to_float(v[(size_t)(row0 + t) * p.ldv + j]) : 0.f;
         float acc = 0.f;
-        if (DK > 0) {
-#pragma unroll
-            for (int i = 0; i < (DK > 0 ? DK : 1); i++) {
-                if (MODE == 0) {
-                    S[i] = fmaf(gh, S[i], cur[dk + i] * vj);
-                    acc = fmaf(S[i], cur[i], acc);
-                } else {
-                    const float kv = cur[dk + i] * vj;
-                    acc = fmaf(cur[i], fmaf(uu[i], kv, S[i]), acc);
-                    S[i] = fmaf(cur[2 * dk + i], S[i], kv);
-                }
+        for (int i = 0; i < dk; i++) {
+            float s = S[(size_t)i * sstride];
+            if (MODE == 0) {
+                s = fmaf(gh, s, cur[dk + i] * vj);
+                acc = fmaf(s, cur[i], acc);
+            } else {
+                const float kv = cur[dk + i] * vj;
+                acc = fmaf(cur[i], fmaf(us[i], kv, s), acc);
+                s = fmaf(cur[2 * dk + i], s, kv);
             }
-        } else {
-            for (int i = 0; i < dk; i++) {
-                float s = S[(size_t)i * sstride];
-                if (MODE == 0) {
-                    s = fmaf(gh, s, cur[dk + i] * vj);
-                    acc = fmaf(s, cur[i], acc);
-                } else {
-                    const float kv = cur[dk + i] * vj;
-                    acc = fmaf(cur[i], fmaf(uu[i], kv, s), acc);
-                    s = fmaf(cur[2 * dk + i], s, kv);
-                }
-                S[(size_t)i * sstride] = s;
-            }
+            S[(size_t)i * sstride] = s;
         }
         if (WRITE_OUT && live) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = acc;
         __syncthreads();
@@ -119,7 +172,10 @@ scan_kernel(ScanParams p) {
     const int dk = DK > 0 ? DK : p.dk;
     const int nvec = MODE == 0 ? 2 : 3;
     float* vecs = smem;                                   // [2][nvec][dk]
-    float* shared_state = smem + 2 * nvec * dk;           // [dk][blockDim.x] when DK == 0
+    float* us = smem + 2 * nvec * dk;                     // [dk] the bonus (token decay)
+    float* shared_state = us + (MODE == 1 ? dk : 0);      // [dk][blockDim.x] when DK == 0
+    if (MODE == 1)
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) us[i] = p.u[(size_t)blockIdx.y * dk + i];   // (visible behind the walk's first barrier)
     const int head = blockIdx.y;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = j < p.dv;
@@ -153,8 +209,8 @@ scan_kernel(ScanParams p) {
     const int sstride = DK > 0 ? 1 : blockDim.x;
     for (int i = 0; i < dk; i++) S[(size_t)i * sstride] = (!from_zero && live) ? from[(size_t)i * p.dv + j] : 0.f;
     const float gh = MODE == 0 ? p.decay[head] : 0.f;
-    if (PASS == 1) walk<T, MODE, DK, false>(p, head, j, live, row0, n, S, sstride, vecs, gh);
-    else walk<T, MODE, DK, true>(p, head, j, live, row0, n, S, sstride, vecs, gh);
+    if (PASS == 1) walk<T, MODE, DK, false>(p, head, j, live, row0, n, S, sstride, vecs, us, gh);
+    else walk<T, MODE, DK, true>(p, head, j, live, row0, n, S, sstride, vecs, us, gh);
     if (PASS == 1) {
         float* B = p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv;
         if (live)
@@ -274,7 +330,7 @@ token_shift_kernel(T* __restrict__ mixes, const T* __restrict__ h, long ldh, con
 template <typename T, int MODE, int DK, int PASS>
 int launch_scan(const ScanParams& p, int tiles, int threads, int z, cudaStream_t stream) {
     const int dk = p.dk, nvec = MODE == 0 ? 2 : 3;
-    const size_t smem = ((size_t)2 * nvec * dk + (DK > 0 ? 0 : (size_t)dk * threads)) * sizeof(float);
+    const size_t smem = ((size_t)2 * nvec * dk + (MODE == 1 ? dk : 0) + (DK > 0 ? 0 : (size_t)dk * threads)) * sizeof(float);
     if (smem > 48 * 1024) {
         HYMT2_REQUIRE(smem <= 200 * 1024, "linear_scan: heads of %d key entries are too large", dk);
         cudaFuncSetAttribute(scan_kernel<T, MODE, DK, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

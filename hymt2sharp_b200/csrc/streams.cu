@@ -27,7 +27,8 @@ struct StreamsParams {
     float eps;
 };
 
-template <typename TO, typename TG, bool WRITE, bool READ>
+// V columns a thread and access (4 where the width and the addresses allow 16-byte accesses, else 1).
+template <typename TO, typename TG, bool WRITE, bool READ, int V>
 __global__ void __launch_bounds__(THREADS)
 streams_kernel(StreamsParams p) {
     __shared__ float scratch[33];
@@ -45,48 +46,74 @@ streams_kernel(StreamsParams p) {
     const size_t plane = (size_t)p.tokens * W;
     float* row = p.X + t * W;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += THREADS) {
-        float x[MAX_STREAMS];
+    for (int c = threadIdx.x * V; c < W; c += THREADS * V) {
+        Pack<float, V> x[MAX_STREAMS];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++) x[s] = s < S ? row[s * plane + c] : 0.f;
+        for (int s = 0; s < MAX_STREAMS; s++)
+            if (s < S) x[s] = load_pack<float, V>(row + s * plane + c);
         if (WRITE) {
-            float y = 0.f;
+            Pack<float, V> y;
+#pragma unroll
+            for (int e = 0; e < V; e++) y.v[e] = 0.f;
 #pragma unroll
             for (int b = 0; b < MAX_BRANCHES; b++)
-                if (b < p.branches) y = fmaf(p.scale[b], p.branch[b][t * W + c], y);
-            float nx[MAX_STREAMS];
+                if (b < p.branches) {
+                    const Pack<float, V> br = load_pack<float, V>(p.branch[b] + t * W + c);
+#pragma unroll
+                    for (int e = 0; e < V; e++) y.v[e] = fmaf(p.scale[b], br.v[e], y.v[e]);
+                }
+            Pack<float, V> nx[MAX_STREAMS];
 #pragma unroll
             for (int r = 0; r < MAX_STREAMS; r++) {
-                if (r >= S) { nx[r] = 0.f; continue; }
+                if (r >= S) continue;
+#pragma unroll
+                for (int e = 0; e < V; e++) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; s++)
+                        if (s < S) a = fmaf(s_mix[s * S + r], x[s].v[e], a);
+                    nx[r].v[e] = fmaf(s_out[r], y.v[e], a);
+                }
+                store_pack<float, V>(row + r * plane + c, nx[r]);
+            }
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; s++)
+                if (s < S) x[s] = nx[s];
+        }
+        if (READ) {
+            Pack<float, V> u;
+#pragma unroll
+            for (int e = 0; e < V; e++) {
                 float a = 0.f;
 #pragma unroll
                 for (int s = 0; s < MAX_STREAMS; s++)
-                    if (s < S) a = fmaf(s_mix[s * S + r], x[s], a);
-                nx[r] = fmaf(s_out[r], y, a);
-                row[r * plane + c] = nx[r];
+                    if (s < S) a = fmaf(s_in[s], x[s].v[e], a);
+                u.v[e] = a;
+                ss = fmaf(a, a, ss);
             }
-#pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++) x[s] = nx[s];
-        }
-        if (READ) {
-            float u = 0.f;
-#pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++)
-                if (s < S) u = fmaf(s_in[s], x[s], u);
-            if (p.gain == nullptr) ((float*)p.out)[t * W + c] = u;
-            else ss = fmaf(u, u, ss);
+            if (p.gain == nullptr) store_pack<float, V>((float*)p.out + t * W + c, u);
         }
     }
     if (!READ || p.gain == nullptr) return;
     ss = block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(ss / (float)W + p.eps);
     // the same thread wrote the entries that it reads here again
-    for (int c = threadIdx.x; c < W; c += THREADS) {
-        float u = 0.f;
+    for (int c = threadIdx.x * V; c < W; c += THREADS * V) {
+        Pack<float, V> u;
+#pragma unroll
+        for (int e = 0; e < V; e++) u.v[e] = 0.f;
 #pragma unroll
         for (int s = 0; s < MAX_STREAMS; s++)
-            if (s < S) u = fmaf(s_in[s], row[s * plane + c], u);
-        ((TO*)p.out)[t * W + c] = from_float<TO>(u * r * to_float(((const TG*)p.gain)[c]));
+            if (s < S) {
+                const Pack<float, V> xs = load_pack<float, V>(row + s * plane + c);
+#pragma unroll
+                for (int e = 0; e < V; e++) u.v[e] = fmaf(s_in[s], xs.v[e], u.v[e]);
+            }
+        const Pack<TG, V> g = load_pack<TG, V>((const TG*)p.gain + c);
+        Pack<TO, V> o;
+#pragma unroll
+        for (int e = 0; e < V; e++) o.v[e] = from_float<TO>(u.v[e] * r * to_float(g.v[e]));
+        store_pack<TO, V>((TO*)p.out + t * W + c, o);
     }
 }
 
@@ -139,10 +166,19 @@ HYMT2_API int hymt2_streams_step(float* X, int streams, int tokens, int width, c
     for (int b = 0; b < p.branches; b++) { p.branch[b] = branches[b]; p.scale[b] = scales[b]; }
     p.gain = gain; p.out = out; p.streams = streams; p.tokens = tokens; p.width = width; p.eps = eps;
     if (!gain) gain_dtype = HYMT2_F32;
+    // 16-byte accesses: the width a multiple of 4 (rows and planes then start on multiples of 4 entries) and every base aligned
+    bool wide = width % 4 == 0 && (uintptr_t)X % 16 == 0 && (!out || (uintptr_t)out % 16 == 0) && (!gain || (uintptr_t)gain % 16 == 0);
+    for (int b = 0; b < p.branches; b++) wide = wide && (uintptr_t)p.branch[b] % 16 == 0;
     HYMT2_DISPATCH_DTYPE(out_dtype, TO, HYMT2_DISPATCH_DTYPE(gain_dtype, TG, {
-        if (write && read) launch_pdl(streams_kernel<TO, TG, true, true>, dim3(tokens), dim3(THREADS), 0, stream, p);
-        else if (write) launch_pdl(streams_kernel<TO, TG, true, false>, dim3(tokens), dim3(THREADS), 0, stream, p);
-        else launch_pdl(streams_kernel<TO, TG, false, true>, dim3(tokens), dim3(THREADS), 0, stream, p);
+        if (wide) {
+            if (write && read) launch_pdl(streams_kernel<TO, TG, true, true, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            else if (write) launch_pdl(streams_kernel<TO, TG, true, false, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            else launch_pdl(streams_kernel<TO, TG, false, true, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
+        } else {
+            if (write && read) launch_pdl(streams_kernel<TO, TG, true, true, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            else if (write) launch_pdl(streams_kernel<TO, TG, true, false, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            else launch_pdl(streams_kernel<TO, TG, false, true, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
+        }
     }));
     return hymt2_check_launch("streams_step");
 }
