@@ -5,7 +5,8 @@
 //   token decay    o_t = (S + diag(u_h) k_t v_t^T)^T r_t;    S = diag(w_t) S + k_t v_t^T      (w_t = exp(-exp(x_t + w0)) per channel)
 //
 // Both forms are independent per value column j of S, so a block owns a tile of columns of one (sequence, head) and a thread
-// one column: S[:, j] in registers where dk is one of the sizes compiled for, in shared memory otherwise.  Everything that
+// one column: S[:, j] in registers where dk is one of the sizes compiled for (columns of 128 rows in two halves, on two threads
+// whose sums meet in shared memory), in shared memory otherwise.  Everything that
 // enters the recurrence is float32; q, k, v arrive in the engine's compute type.  The scan writes o as float32; the norm of
 // each head's o, the gain and the gate follow in `head_norm_gate`.
 //
@@ -56,9 +57,11 @@ struct ScanParams {
 // bonus (token decay).  With DK > 0 (state in registers) the next token's vectors are loaded into registers in front of the
 // current token's sums and stored to shared memory behind them, so that the loads' latency lies under the arithmetic; the
 // vectors are read back four entries at a time, and o is summed in four partial sums over i mod 4, added as (0 + 1) + (2 + 3).
-template <typename T, int MODE, int DK, bool WRITE_OUT>
+// SPLIT threads share a column: thread `part` holds rows part * DK / SPLIT onward, the parts' sums of o meet in `partial`
+// (shared, [2][SPLIT][columns]) and part 0 adds them in ascending order behind the token's barrier.
+template <typename T, int MODE, int DK, int SPLIT, bool WRITE_OUT>
 __device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool live, int row0, int n, float* S, int sstride,
-                                     float* vecs, const float* us, float gh) {
+                                     float* vecs, const float* us, float gh, int part, int cols, float* partial) {
     const int dk = DK > 0 ? DK : p.dk;
     const int nvec = MODE == 0 ? 2 : 3;              // q, k (, w) per token
     const T* q = (const T*)p.q + (size_t)head * dk;
@@ -100,13 +103,14 @@ __device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool 
                 }
                 if (live) vnext = to_float(v[r * p.ldv + j]);
             }
-            const float4* cq = reinterpret_cast<const float4*>(cur);
-            const float4* ck = reinterpret_cast<const float4*>(cur + dk);
-            const float4* cw = reinterpret_cast<const float4*>(cur + 2 * dk);
-            const float4* cu = reinterpret_cast<const float4*>(us);
+            constexpr int ROWS = (DK > 0 ? DK : 4) / SPLIT;
+            const float4* cq = reinterpret_cast<const float4*>(cur) + part * (ROWS / 4);
+            const float4* ck = reinterpret_cast<const float4*>(cur + dk) + part * (ROWS / 4);
+            const float4* cw = reinterpret_cast<const float4*>(cur + 2 * dk) + part * (ROWS / 4);
+            const float4* cu = reinterpret_cast<const float4*>(us) + part * (ROWS / 4);
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int g = 0; g < (DK > 0 ? DK : 4) / 4; g++) {
+            for (int g = 0; g < ROWS / 4; g++) {
                 const float4 q4 = cq[g], k4 = ck[g];
                 float* s = S + 4 * g;
                 if (MODE == 0) {
@@ -135,8 +139,22 @@ __device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool 
                     }
                 }
             }
-            if (WRITE_OUT && live) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = (a0 + a1) + (a2 + a3);
-            __syncthreads();
+            const float mine = (a0 + a1) + (a2 + a3);
+            if constexpr (SPLIT == 1) {
+                if (WRITE_OUT && live) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = mine;
+                __syncthreads();
+            } else {
+                float* meet = partial + (size_t)(t & 1) * SPLIT * cols;
+                const int col = threadIdx.x - part * cols;
+                if (WRITE_OUT) meet[part * cols + col] = mine;
+                __syncthreads();
+                if (WRITE_OUT && live && part == 0) {
+                    float o = meet[col];
+#pragma unroll
+                    for (int r = 1; r < SPLIT; r++) o += meet[r * cols + col];
+                    p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = o;
+                }
+            }
         }
         return;
     }
@@ -173,11 +191,15 @@ scan_kernel(ScanParams p) {
     const int nvec = MODE == 0 ? 2 : 3;
     float* vecs = smem;                                   // [2][nvec][dk]
     float* us = smem + 2 * nvec * dk;                     // [dk] the bonus (token decay)
-    float* shared_state = us + (MODE == 1 ? dk : 0);      // [dk][blockDim.x] when DK == 0
+    constexpr int SPLIT = DK == 128 ? 2 : 1;              // threads that share a column (each holds DK / SPLIT rows of it)
+    float* partial = us + (MODE == 1 ? dk : 0);           // [2][SPLIT][columns] when SPLIT > 1
+    float* shared_state = partial;                        // [dk][blockDim.x] when DK == 0
     if (MODE == 1)
         for (int i = threadIdx.x; i < dk; i += blockDim.x) us[i] = p.u[(size_t)blockIdx.y * dk + i];   // (visible behind the walk's first barrier)
     const int head = blockIdx.y;
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int cols = blockDim.x / SPLIT;
+    const int part = threadIdx.x / cols;
+    const int j = blockIdx.x * cols + (threadIdx.x - part * cols);
     const bool live = j < p.dv;
     int seq, row0, n, chunk = 0;
     bool from_zero, keep;
@@ -198,23 +220,36 @@ scan_kernel(ScanParams p) {
     if (n <= 0) return;
     const int slot = p.slot_ids[seq];
     if (slot < 0) {                                       // a padding row: zeros out, nothing remembered
-        if (PASS != 1 && live)
+        if (PASS != 1 && live && part == 0)
             for (int t = 0; t < n; t++) p.out[(size_t)(row0 + t) * p.heads * p.dv + (size_t)head * p.dv + j] = 0.f;
         return;
     }
     float* st = reinterpret_cast<float*>(p.state + (size_t)slot * p.state_stride + p.state_offset) + (size_t)head * dk * p.dv;
     const float* from = PASS == 3 ? p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv : st;   // pass 2 left S_c in chunk_B
-    float reg[DK > 0 ? DK : 1];
+    constexpr int ROWS = DK > 0 ? DK / SPLIT : 1;         // rows of the column that this thread holds (DK == 0: all dk, in shared memory)
+    const int rows = DK > 0 ? ROWS : dk, i0 = part * ROWS;
+    float reg[ROWS];
     float* S = DK > 0 ? reg : shared_state + threadIdx.x;
     const int sstride = DK > 0 ? 1 : blockDim.x;
-    for (int i = 0; i < dk; i++) S[(size_t)i * sstride] = (!from_zero && live) ? from[(size_t)i * p.dv + j] : 0.f;
+    if (DK > 0) {
+#pragma unroll
+        for (int i = 0; i < ROWS; i++) reg[i] = (!from_zero && live) ? from[(size_t)(i0 + i) * p.dv + j] : 0.f;
+    } else {
+        for (int i = 0; i < dk; i++) S[(size_t)i * sstride] = (!from_zero && live) ? from[(size_t)i * p.dv + j] : 0.f;
+    }
     const float gh = MODE == 0 ? p.decay[head] : 0.f;
-    if (PASS == 1) walk<T, MODE, DK, false>(p, head, j, live, row0, n, S, sstride, vecs, us, gh);
-    else walk<T, MODE, DK, true>(p, head, j, live, row0, n, S, sstride, vecs, us, gh);
+    if (PASS == 1) walk<T, MODE, DK, SPLIT, false>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
+    else walk<T, MODE, DK, SPLIT, true>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
     if (PASS == 1) {
         float* B = p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv;
-        if (live)
-            for (int i = 0; i < dk; i++) B[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+        if (live) {
+            if (DK > 0) {
+#pragma unroll
+                for (int i = 0; i < ROWS; i++) B[(size_t)(i0 + i) * p.dv + j] = reg[i];
+            } else {
+                for (int i = 0; i < rows; i++) B[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+            }
+        }
         if (MODE == 1 && blockIdx.x == 0) {               // the product of the chunk's decays per channel, in token order
             float* A = p.chunk_A + ((size_t)chunk * p.heads + head) * dk;
             for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -225,7 +260,12 @@ scan_kernel(ScanParams p) {
             }
         }
     } else if (keep && live) {
-        for (int i = 0; i < dk; i++) st[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < ROWS; i++) st[(size_t)(i0 + i) * p.dv + j] = reg[i];
+        } else {
+            for (int i = 0; i < rows; i++) st[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
+        }
     }
 }
 
@@ -249,19 +289,36 @@ scan_carry_kernel(ScanParams p) {
     float s = p.kv_lens[seq] - n == 0 ? 0.f : st[e];
     const int i = e / p.dv;
     const float gh = MODE == 0 ? p.decay[head] : 0.f;
-    for (int c = c0; c < c1; c++) {
-        float* B = p.chunk_B + ((size_t)c * p.heads + head) * per;
-        const float b = B[e];
-        B[e] = s;
-        float a;
-        if (MODE == 0) {
-            a = 1.f;
-            const int len = p.chunk_len[c];
-            for (int t = 0; t < len; t++) a *= gh;
-        } else {
-            a = p.chunk_A[((size_t)c * p.heads + head) * p.dk + i];
+    // fixed decay: a chunk's factor is the decay multiplied up over its tokens; all chunks but a sequence's last have the first
+    // one's length, so that product is made once.  The loads of AHEAD chunks are issued together in front of their serial sums.
+    constexpr int AHEAD = 4;
+    const int len0 = p.chunk_len[c0];
+    float a_first = 1.f;
+    if (MODE == 0)
+        for (int t = 0; t < len0; t++) a_first *= gh;
+    for (int c = c0; c < c1; c += AHEAD) {
+        float a[AHEAD], b[AHEAD];
+#pragma unroll
+        for (int r = 0; r < AHEAD; r++) {
+            if (c + r >= c1) continue;
+            b[r] = p.chunk_B[((size_t)(c + r) * p.heads + head) * per + e];
+            if (MODE == 0) {
+                const int len = p.chunk_len[c + r];
+                a[r] = a_first;
+                if (len != len0) {
+                    a[r] = 1.f;
+                    for (int t = 0; t < len; t++) a[r] *= gh;
+                }
+            } else {
+                a[r] = p.chunk_A[((size_t)(c + r) * p.heads + head) * p.dk + i];
+            }
         }
-        s = fmaf(a, s, b);
+#pragma unroll
+        for (int r = 0; r < AHEAD; r++) {
+            if (c + r >= c1) continue;
+            p.chunk_B[((size_t)(c + r) * p.heads + head) * per + e] = s;
+            s = fmaf(a[r], s, b[r]);
+        }
     }
     st[e] = s;
 }
@@ -328,9 +385,11 @@ token_shift_kernel(T* __restrict__ mixes, const T* __restrict__ h, long ldh, con
 }
 
 template <typename T, int MODE, int DK, int PASS>
-int launch_scan(const ScanParams& p, int tiles, int threads, int z, cudaStream_t stream) {
+int launch_scan(const ScanParams& p, int threads, int z, cudaStream_t stream) {
+    const int cols = DK == 128 ? threads / 2 : threads;   // (the kernel's SPLIT)
+    const int tiles = (p.dv + cols - 1) / cols;
     const int dk = p.dk, nvec = MODE == 0 ? 2 : 3;
-    const size_t smem = ((size_t)2 * nvec * dk + (MODE == 1 ? dk : 0) + (DK > 0 ? 0 : (size_t)dk * threads)) * sizeof(float);
+    const size_t smem = ((size_t)2 * nvec * dk + (MODE == 1 ? dk : 0) + (DK > 0 ? (size_t)2 * threads : (size_t)dk * threads)) * sizeof(float);
     if (smem > 48 * 1024) {
         HYMT2_REQUIRE(smem <= 200 * 1024, "linear_scan: heads of %d key entries are too large", dk);
         cudaFuncSetAttribute(scan_kernel<T, MODE, DK, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -343,13 +402,12 @@ template <typename T, int MODE, int PASS>
 int launch_scan_dk(const ScanParams& p, int z, cudaStream_t stream) {
     // columns a block: enough blocks to fill the device matter more than wide blocks
     const int threads = p.dv >= 64 ? 64 : 32;
-    const int tiles = (p.dv + threads - 1) / threads;
     switch (p.dk) {
-        case 16: return launch_scan<T, MODE, 16, PASS>(p, tiles, threads, z, stream);
-        case 32: return launch_scan<T, MODE, 32, PASS>(p, tiles, threads, z, stream);
-        case 64: return launch_scan<T, MODE, 64, PASS>(p, tiles, threads, z, stream);
-        case 128: return launch_scan<T, MODE, 128, PASS>(p, tiles, threads, z, stream);
-        default: return launch_scan<T, MODE, 0, PASS>(p, tiles, threads, z, stream);
+        case 16: return launch_scan<T, MODE, 16, PASS>(p, threads, z, stream);
+        case 32: return launch_scan<T, MODE, 32, PASS>(p, threads, z, stream);
+        case 64: return launch_scan<T, MODE, 64, PASS>(p, threads, z, stream);
+        case 128: return launch_scan<T, MODE, 128, PASS>(p, p.dv > 16 ? 64 : 32, z, stream);   // two threads a column: 32 or 16 columns a block
+        default: return launch_scan<T, MODE, 0, PASS>(p, threads, z, stream);
     }
 }
 
