@@ -68,6 +68,7 @@ class Linear:
 
 
 TC_BATCH_MIN_TOKENS = 128   # from this many tokens on, a batch of small products goes to the tensor cores one by one,
+TC_ALWAYS_MIN_WEIGHT = 512 * 512  # from this size of w[z] on, the tensor-core kernel at every number of tokens
 TC_BATCH_MIN_WEIGHT = 256 * 256   # if each of them is large enough to be worth a launch of its own (entries of w[z])
 
 
@@ -77,15 +78,22 @@ def matmul_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, x_step: 
     one CUDA-core launch for the whole batch, a warp per output column, which reads w once.  Many tokens: one tensor-core
     product per z where the kernel takes the operands.  Between the two: one CUDA-core launch in tiles."""
     batch, N, K = w.shape
-    if x.shape[0] <= ops.SKINNY_MAX_ROWS and x.dtype == w.dtype:
+    both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    # products as large as a layer's own projections (time mixing's four) stream their weights best through the tensor-core
+    # kernel at every number of tokens; a launch each costs less than the batched CUDA-core kernels lose on them
+    large = both_bf16 and N * K >= TC_ALWAYS_MIN_WEIGHT
+    if x.shape[0] <= ops.SKINNY_MAX_ROWS and x.dtype == w.dtype and not large:
         ops.gemm_skinny_batched(out, x, w, x_step, out_step)
         return
-    if x.shape[0] >= TC_BATCH_MIN_TOKENS and N * K >= TC_BATCH_MIN_WEIGHT and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+    if (x.shape[0] >= TC_BATCH_MIN_TOKENS or large) and N * K >= TC_BATCH_MIN_WEIGHT and both_bf16:
         views = [(out[:, z * out_step: z * out_step + N], x[:, z * x_step: z * x_step + K], w[z]) for z in range(batch)]
         if all(ops.gemm_tc_supported(o, a, b, ops.EPILOGUE_STORE) for o, a, b in views[:2]) and (x_step * 2) % 16 == 0:
             for o, a, b in views:
                 ops.gemm_tc(o, a, b, ops.EPILOGUE_STORE, ops.device_status(o.device), checked=True)
             return
+    if x.shape[0] <= ops.SKINNY_MAX_ROWS and x.dtype == w.dtype:
+        ops.gemm_skinny_batched(out, x, w, x_step, out_step)
+        return
     ops.gemm_simt_batched(out, x, w, batch, x_step, out_step)
 
 
