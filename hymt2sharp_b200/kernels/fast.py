@@ -108,6 +108,9 @@ def try_attention_kv(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, dv,
     bt = k_plane.shape[2]
     if out.dtype != torch.bfloat16 or d not in (64, 128) or dv not in (64, 128) or bt & (bt - 1):
         return False
+    if not sink and d == dv:
+        # nothing here that the classic kernels do not take: among them the tcgen05 decode kernel for heads of 128
+        return try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window)
     if ctx.decode:
         splits = max(1, -(-ctx.max_kv_len // DECODE_CHUNK_KEYS))
         na, nm = ops.attention_simt_scratch(ctx.num_tokens, nh, dv, splits)
