@@ -199,8 +199,10 @@ def _time_mix(hidden, heads, dim, rank):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden, heads, dim, rank", [(44, 3, 5, 3), (64, 2, 32, 16), (128, 2, 64, 8), (96, 1, 16, 1), (256, 2, 128, 32), (40, 1, 24, None)])
+@pytest.mark.parametrize("hidden, heads, dim, rank", [(44, 3, 5, 3), (64, 2, 32, 16), (128, 2, 64, 8), (96, 1, 16, 1), (256, 2, 128, 32), (40, 1, 24, None),
+                                                      (512, 8, 64, 16)])
 def test_time_mixing_in_prompts_portions_decoding_and_batches(dtype, hidden, heads, dim, rank):
+    """(The last shape's four projections are large enough for the tensor-core kernel at every number of tokens.)"""
     torch.manual_seed(hidden + dim)
     part = _time_mix(hidden, heads, dim, rank)
     w = _weights(part, 0.15)
