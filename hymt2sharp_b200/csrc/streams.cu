@@ -27,8 +27,9 @@ struct StreamsParams {
     float eps;
 };
 
-// V columns a thread and access (4 where the width and the addresses allow 16-byte accesses, else 1).
-template <typename TO, typename TG, bool WRITE, bool READ, int V>
+// V columns a thread and access (4 where the width and the addresses allow 16-byte accesses, else 1); SM: the most streams that
+// the instance holds in registers (2, 4 or MAX_STREAMS: the fewer, the more blocks an SM keeps in flight).
+template <typename TO, typename TG, bool WRITE, bool READ, int V, int SM>
 __global__ void __launch_bounds__(THREADS)
 streams_kernel(StreamsParams p) {
     __shared__ float scratch[33];
@@ -47,9 +48,9 @@ streams_kernel(StreamsParams p) {
     float* row = p.X + t * W;
     float ss = 0.f;
     for (int c = threadIdx.x * V; c < W; c += THREADS * V) {
-        Pack<float, V> x[MAX_STREAMS];
+        Pack<float, V> x[SM];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++)
+        for (int s = 0; s < SM; s++)
             if (s < S) x[s] = load_pack<float, V>(row + s * plane + c);
         if (WRITE) {
             Pack<float, V> y;
@@ -62,22 +63,22 @@ streams_kernel(StreamsParams p) {
 #pragma unroll
                     for (int e = 0; e < V; e++) y.v[e] = fmaf(p.scale[b], br.v[e], y.v[e]);
                 }
-            Pack<float, V> nx[MAX_STREAMS];
+            Pack<float, V> nx[SM];
 #pragma unroll
-            for (int r = 0; r < MAX_STREAMS; r++) {
+            for (int r = 0; r < SM; r++) {
                 if (r >= S) continue;
 #pragma unroll
                 for (int e = 0; e < V; e++) {
                     float a = 0.f;
 #pragma unroll
-                    for (int s = 0; s < MAX_STREAMS; s++)
+                    for (int s = 0; s < SM; s++)
                         if (s < S) a = fmaf(s_mix[s * S + r], x[s].v[e], a);
                     nx[r].v[e] = fmaf(s_out[r], y.v[e], a);
                 }
                 store_pack<float, V>(row + r * plane + c, nx[r]);
             }
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++)
+            for (int s = 0; s < SM; s++)
                 if (s < S) x[s] = nx[s];
         }
         if (READ) {
@@ -86,7 +87,7 @@ streams_kernel(StreamsParams p) {
             for (int e = 0; e < V; e++) {
                 float a = 0.f;
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; s++)
+                for (int s = 0; s < SM; s++)
                     if (s < S) a = fmaf(s_in[s], x[s].v[e], a);
                 u.v[e] = a;
                 ss = fmaf(a, a, ss);
@@ -103,7 +104,7 @@ streams_kernel(StreamsParams p) {
 #pragma unroll
         for (int e = 0; e < V; e++) u.v[e] = 0.f;
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++)
+        for (int s = 0; s < SM; s++)
             if (s < S) {
                 const Pack<float, V> xs = load_pack<float, V>(row + s * plane + c);
 #pragma unroll
@@ -169,16 +170,23 @@ HYMT2_API int hymt2_streams_step(float* X, int streams, int tokens, int width, c
     // 16-byte accesses: the width a multiple of 4 (rows and planes then start on multiples of 4 entries) and every base aligned
     bool wide = width % 4 == 0 && (uintptr_t)X % 16 == 0 && (!out || (uintptr_t)out % 16 == 0) && (!gain || (uintptr_t)gain % 16 == 0);
     for (int b = 0; b < p.branches; b++) wide = wide && (uintptr_t)p.branch[b] % 16 == 0;
+#define HYMT2_STREAMS_LAUNCH(V, SM)                                                                                               \
+    do {                                                                                                                          \
+        if (write && read) launch_pdl(streams_kernel<TO, TG, true, true, V, SM>, dim3(tokens), dim3(THREADS), 0, stream, p);      \
+        else if (write) launch_pdl(streams_kernel<TO, TG, true, false, V, SM>, dim3(tokens), dim3(THREADS), 0, stream, p);        \
+        else launch_pdl(streams_kernel<TO, TG, false, true, V, SM>, dim3(tokens), dim3(THREADS), 0, stream, p);                   \
+    } while (0)
     HYMT2_DISPATCH_DTYPE(out_dtype, TO, HYMT2_DISPATCH_DTYPE(gain_dtype, TG, {
         if (wide) {
-            if (write && read) launch_pdl(streams_kernel<TO, TG, true, true, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
-            else if (write) launch_pdl(streams_kernel<TO, TG, true, false, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
-            else launch_pdl(streams_kernel<TO, TG, false, true, 4>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            if (streams <= 2) HYMT2_STREAMS_LAUNCH(4, 2);
+            else if (streams <= 4) HYMT2_STREAMS_LAUNCH(4, 4);
+            else HYMT2_STREAMS_LAUNCH(4, MAX_STREAMS);
         } else {
-            if (write && read) launch_pdl(streams_kernel<TO, TG, true, true, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
-            else if (write) launch_pdl(streams_kernel<TO, TG, true, false, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
-            else launch_pdl(streams_kernel<TO, TG, false, true, 1>, dim3(tokens), dim3(THREADS), 0, stream, p);
+            if (streams <= 2) HYMT2_STREAMS_LAUNCH(1, 2);
+            else if (streams <= 4) HYMT2_STREAMS_LAUNCH(1, 4);
+            else HYMT2_STREAMS_LAUNCH(1, MAX_STREAMS);
         }
     }));
+#undef HYMT2_STREAMS_LAUNCH
     return hymt2_check_launch("streams_step");
 }
