@@ -352,6 +352,57 @@ head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T*
     }
 }
 
+// The same with a head's entries in registers: lane l holds entries [128 p + 4 l, 128 p + 4 l + 4) for p < P, read once in
+// 16-byte accesses; the gate and the output move four entries an access.
+template <typename T, int P>
+__global__ void __launch_bounds__(128)
+head_norm_gate_wide_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, long ldg,
+                           const float* __restrict__ weight, long items, int heads, int dv, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const long t = item / heads;
+    const int head = (int)(item % heads);
+    const float* row = o + (size_t)item * dv;
+    Pack<float, 4> x[P];
+    Pack<T, 4> g[P];
+    float ss = 0.f;
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+        const int c = p * 128 + lane * 4;
+        if (c < dv) {
+            x[p] = load_pack<float, 4>(row + c);
+            if (gate) g[p] = load_pack<T, 4>(gate + (size_t)t * ldg + (size_t)head * dv + c);
+#pragma unroll
+            for (int e = 0; e < 4; e++) ss = fmaf(x[p].v[e], x[p].v[e], ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)dv + eps);
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+        const int c = p * 128 + lane * 4;
+        if (c < dv) {
+            Pack<float, 4> w;
+            if (weight) w = load_pack<float, 4>(weight + (size_t)head * dv + c);
+            Pack<T, 4> y;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float v = x[p].v[e] * r;
+                if (weight) v *= w.v[e];
+                if (gate) {
+                    const float gv = to_float(g[p].v[e]);
+                    v *= gv / (1.0f + expf(-gv));
+                }
+                y.v[e] = from_float<T>(v);
+            }
+            store_pack<T, 4>(out + (size_t)item * dv + c, y);
+        }
+    }
+}
+
 // mixes[t][s * width + c] = h[t][c] + (h[t-1][c] - h[t][c]) * mu[s][c]; a sequence's first new token takes h[t-1] from the state
 // row (zeros at position 0), and the thread of that token also writes the step's last h there: one thread reads and renews.
 template <typename T>
@@ -457,8 +508,20 @@ HYMT2_API int hymt2_head_norm_gate(void* out, const float* o, const void* gate, 
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && heads > 0 && dv > 0, "head_norm_gate: bad sizes");
     const long items = (long)tokens * heads;
-    HYMT2_DISPATCH_DTYPE(dtype, T, (launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, o,
-                                               (const T*)gate, ldg, weight, items, heads, dv, eps)));
+    const dim3 grid((unsigned)((items + 3) / 4));
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        // a head in registers, four entries an access: widths that are multiples of 4 up to 512, every row start aligned
+        const bool wide = dv % 4 == 0 && dv <= 512 && (uintptr_t)o % 16 == 0 && (uintptr_t)out % (4 * sizeof(T)) == 0 &&
+                          (!gate || ((uintptr_t)gate % (4 * sizeof(T)) == 0 && ldg % 4 == 0)) && (!weight || (uintptr_t)weight % 16 == 0);
+        if (wide && dv <= 128)
+            launch_pdl(head_norm_gate_wide_kernel<T, 1>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+        else if (wide && dv <= 256)
+            launch_pdl(head_norm_gate_wide_kernel<T, 2>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+        else if (wide)
+            launch_pdl(head_norm_gate_wide_kernel<T, 4>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+        else
+            launch_pdl(head_norm_gate_kernel<T>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+    });
     return hymt2_check_launch("head_norm_gate");
 }
 

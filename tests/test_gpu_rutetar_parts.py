@@ -156,6 +156,31 @@ def test_retention_in_prompts_portions_decoding_and_batches(dtype, hidden, heads
                 helpers.assert_close(g.numpy(), refs[i][:g.shape[0]], _name(dtype), f"retention {what}, sequence {i}", factor=2.0)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, dv, shift", [(3, 4, 0), (2, 36, 0), (2, 128, 0), (1, 132, 0), (2, 256, 4), (1, 300, 0), (2, 512, 0), (1, 516, 0),
+                                              (3, 7, 0), (2, 64, 3), (2, 10, 0)])
+def test_head_norm_with_gain_and_gate_at_every_width(dtype, heads, dv, shift):
+    """A head's output over its root mean square, times a gain, times silu(gate): heads that a lane holds in one, two and four
+    16-byte pieces, heads wider than that, widths that are no multiple of 4, and a gate that is a column range of a wider
+    matrix starting at an aligned or an odd column."""
+    from hymt2sharp_b200.kernels import ops
+    g = torch.Generator().manual_seed(dv * 7 + heads)
+    T, D = 37, heads * dv
+    o = torch.randn(T, D, generator=g) * torch.rand(T, 1, generator=g) * 5
+    wide = torch.randn(T, shift + D + (4 if shift == 4 else 5), generator=g).to(dtype)   # rows of 4 k entries keep the wide form
+    gain = 1 + 0.3 * torch.randn(D, generator=g)
+    for use_gain, use_gate in ((True, True), (False, True), (True, False), (False, False)):
+        want = plain.unit_rms(o.to(F64).reshape(T, heads, dv), 1e-5).reshape(T, D)
+        if use_gain:
+            want = want * gain.to(F64)
+        if use_gate:
+            want = want * plain.silu(wide[:, shift:shift + D].to(F64))
+        out = torch.full((T, D), float("nan"), dtype=dtype, device=DEV)
+        gate = wide.to(DEV)[:, shift:shift + D] if use_gate else None
+        ops.head_norm_gate(out, o.to(DEV), gate, gain.to(DEV) if use_gain else None, heads, dv, 1e-5)
+        helpers.assert_close(out.double().cpu(), want, _name(dtype), f"head norm heads={heads} dv={dv} gain={use_gain} gate={use_gate}")
+
+
 def test_retention_remembers_a_far_token_and_forgets_at_its_rate():
     """One token's key and value stand out among hundreds; with a decay of 1 - 2^-10 it is still there 600 tokens on (in the
     prompt's chunks and in decoded steps), with 0.9 it is gone: queries that point at the key read decay^distance * value."""
