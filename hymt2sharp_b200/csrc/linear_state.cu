@@ -180,6 +180,116 @@ __device__ __forceinline__ void walk(const ScanParams& p, int head, int j, bool 
     }
 }
 
+// Pass 1 with the state in registers: a chunk's contribution to the state from zero has no token-by-token dependency,
+//     B[i][j] = sum_t c_t[i] v_t[j],   c_t[i] = k_t[i] * (the product of the decays of the tokens behind t in the chunk)[i],
+// so groups of GATHER_TOKENS tokens are staged at once (all their loads in flight together), from the chunk's last group to
+// its first, with the product of the decays carried from group to group: fixed decay, a scalar; token decay, a register per
+// key entry that a thread owns, which at the end is the chunk's whole product (returned through `A` when given).  One fused
+// multiply-add an entry and token.  `kp` and `wv` are shared memory of GATHER_TOKENS * dk floats each (fixed decay: `wv`
+// holds the decay's first GATHER_TOKENS powers).
+constexpr int GATHER_TOKENS = 8;
+
+template <typename T, int MODE, int DK, int SPLIT>
+__device__ __forceinline__ void gather(const ScanParams& p, int head, int j, bool live, int row0, int n, float* S, float* kp, float* wv,
+                                       float gh, int part, float* A) {
+    constexpr int TB = GATHER_TOKENS, ROWS = DK / SPLIT;
+    constexpr int OWN = (DK + 31) / 32;               // key entries that one thread owns (blocks of 32 or more threads)
+    const T* k = (const T*)p.k + (size_t)head * DK;
+    const T* v = (const T*)p.v + (size_t)head * p.dv;
+    const float* xx = MODE == 1 ? p.x + (size_t)head * DK : nullptr;
+    const float* w0 = MODE == 1 ? p.w0 + (size_t)head * DK : nullptr;
+    float behind = 1.f;                               // fixed decay: the decay to the power of the tokens behind the group
+    float run[OWN];                                   // token decay: the product of the decays behind the group, per owned entry
+#pragma unroll
+    for (int e = 0; e < OWN; e++) run[e] = 1.f;
+    if (MODE == 0) {                                  // fixed decay: wv[d] = decay^d for the tokens behind one inside its group
+        if (threadIdx.x < TB) {
+            float f = 1.f;
+            for (int b = 0; b < (int)threadIdx.x; b++) f *= gh;
+            wv[threadIdx.x] = f;
+        }
+        __syncthreads();
+    }
+    for (int g1 = n; g1 > 0; g1 -= TB) {
+        const int g0 = g1 > TB ? g1 - TB : 0, len = g1 - g0;
+        const float scale_behind = p.k_scale * behind;
+        float vv[TB];
+#pragma unroll
+        for (int tt = 0; tt < TB; tt++) vv[tt] = (live && tt < len) ? to_float(v[(size_t)(row0 + g0 + tt) * p.ldv + j]) : 0.f;
+        // FLIGHT loads of a thread are issued together in front of their use
+        constexpr int FLIGHT = 8;
+        for (int base = threadIdx.x; base < len * DK; base += FLIGHT * blockDim.x) {
+            T kr[FLIGHT];
+            float xr[FLIGHT];
+#pragma unroll
+            for (int m = 0; m < FLIGHT; m++) {
+                const int e = base + m * blockDim.x;
+                if (e < len * DK) {
+                    const int tt = e / DK, i = e - tt * DK;
+                    const size_t r = (size_t)(row0 + g0 + tt);
+                    kr[m] = k[r * p.ldk + i];
+                    if (MODE == 1) xr[m] = xx[r * p.ldx + i];
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < FLIGHT; m++) {
+                const int e = base + m * blockDim.x;
+                if (e < len * DK) {
+                    const int tt = e / DK, i = e - tt * DK;
+                    if (MODE == 0) {
+                        kp[e] = to_float(kr[m]) * (scale_behind * wv[len - 1 - tt]);
+                    } else {
+                        kp[e] = to_float(kr[m]);
+                        wv[e] = expf(-expf(xr[m] + w0[i]));
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (MODE == 0) {
+            for (int b = 0; b < len; b++) behind *= gh;
+        } else {
+#pragma unroll
+            for (int e = 0; e < OWN; e++) {
+                const int i = threadIdx.x + e * blockDim.x;
+                if (i < DK) {
+                    float w = run[e];
+                    for (int tt = len - 1; tt >= 0; tt--) {
+                        kp[tt * DK + i] *= w;
+                        w *= wv[tt * DK + i];
+                    }
+                    run[e] = w;
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int tt = 0; tt < TB; tt++) {
+            if (tt < len) {
+                const float4* c4 = reinterpret_cast<const float4*>(kp + tt * DK) + part * (ROWS / 4);
+                const float vj = vv[tt];
+#pragma unroll
+                for (int g = 0; g < ROWS / 4; g++) {
+                    const float4 c = c4[g];
+                    float* s = S + 4 * g;
+                    s[0] = fmaf(c.x, vj, s[0]);
+                    s[1] = fmaf(c.y, vj, s[1]);
+                    s[2] = fmaf(c.z, vj, s[2]);
+                    s[3] = fmaf(c.w, vj, s[3]);
+                }
+            }
+        }
+        __syncthreads();                              // the next group overwrites kp
+    }
+    if (MODE == 1 && A) {
+#pragma unroll
+        for (int e = 0; e < OWN; e++) {
+            const int i = threadIdx.x + e * blockDim.x;
+            if (i < DK) A[i] = run[e];
+        }
+    }
+}
+
 // PASS 0: the serial form, grid (column tiles, heads, sequences).  PASS 1 and 3: grid (column tiles, heads, chunks).
 template <typename T, int MODE, int DK, int PASS>
 __global__ void __launch_bounds__(128)
@@ -194,7 +304,7 @@ scan_kernel(ScanParams p) {
     constexpr int SPLIT = DK == 128 ? 2 : 1;              // threads that share a column (each holds DK / SPLIT rows of it)
     float* partial = us + (MODE == 1 ? dk : 0);           // [2][SPLIT][columns] when SPLIT > 1
     float* shared_state = partial;                        // [dk][blockDim.x] when DK == 0
-    if (MODE == 1)
+    if (MODE == 1 && !(PASS == 1 && DK > 0))              // (pass 1 with the state in registers lays the shared memory out anew)
         for (int i = threadIdx.x; i < dk; i += blockDim.x) us[i] = p.u[(size_t)blockIdx.y * dk + i];   // (visible behind the walk's first barrier)
     const int head = blockIdx.y;
     const int cols = blockDim.x / SPLIT;
@@ -238,8 +348,14 @@ scan_kernel(ScanParams p) {
         for (int i = 0; i < dk; i++) S[(size_t)i * sstride] = (!from_zero && live) ? from[(size_t)i * p.dv + j] : 0.f;
     }
     const float gh = MODE == 0 ? p.decay[head] : 0.f;
-    if (PASS == 1) walk<T, MODE, DK, SPLIT, false>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
-    else walk<T, MODE, DK, SPLIT, true>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
+    if constexpr (PASS == 1 && DK > 0) {
+        float* A = (MODE == 1 && blockIdx.x == 0) ? p.chunk_A + ((size_t)chunk * p.heads + head) * dk : nullptr;
+        gather<T, MODE, DK, SPLIT>(p, head, j, live, row0, n, S, smem, smem + GATHER_TOKENS * DK, gh, part, A);
+    } else if (PASS == 1) {
+        walk<T, MODE, DK, SPLIT, false>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
+    } else {
+        walk<T, MODE, DK, SPLIT, true>(p, head, j, live, row0, n, S, sstride, vecs, us, gh, part, cols, partial);
+    }
     if (PASS == 1) {
         float* B = p.chunk_B + ((size_t)chunk * p.heads + head) * dk * p.dv;
         if (live) {
@@ -250,7 +366,7 @@ scan_kernel(ScanParams p) {
                 for (int i = 0; i < rows; i++) B[(size_t)i * p.dv + j] = S[(size_t)i * sstride];
             }
         }
-        if (MODE == 1 && blockIdx.x == 0) {               // the product of the chunk's decays per channel, in token order
+        if (MODE == 1 && DK == 0 && blockIdx.x == 0) {    // the product of the chunk's decays per channel (DK > 0: made above)
             float* A = p.chunk_A + ((size_t)chunk * p.heads + head) * dk;
             for (int i = threadIdx.x; i < dk; i += blockDim.x) {
                 float a = 1.f;
@@ -440,7 +556,8 @@ int launch_scan(const ScanParams& p, int threads, int z, cudaStream_t stream) {
     const int cols = DK == 128 ? threads / 2 : threads;   // (the kernel's SPLIT)
     const int tiles = (p.dv + cols - 1) / cols;
     const int dk = p.dk, nvec = MODE == 0 ? 2 : 3;
-    const size_t smem = ((size_t)2 * nvec * dk + (MODE == 1 ? dk : 0) + (DK > 0 ? (size_t)2 * threads : (size_t)dk * threads)) * sizeof(float);
+    size_t smem = ((size_t)2 * nvec * dk + (MODE == 1 ? dk : 0) + (DK > 0 ? (size_t)2 * threads : (size_t)dk * threads)) * sizeof(float);
+    if (PASS == 1 && DK > 0) smem = (size_t)2 * GATHER_TOKENS * DK * sizeof(float);   // the staged groups (fixed decay: its powers)
     if (smem > 48 * 1024) {
         HYMT2_REQUIRE(smem <= 200 * 1024, "linear_scan: heads of %d key entries are too large", dk);
         cudaFuncSetAttribute(scan_kernel<T, MODE, DK, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
