@@ -45,4 +45,4 @@ def load_config(folder_or_file: str):
 
 def _load_builtin() -> None:
     # the built-in architectures register themselves on import
-    from ..engine import hunyuan_dense, novunex, pemezen, rutetar  # noqa: F401
+    from ..engine import hunyuan_dense, novunex, pemezen, pulenex, rutetar  # noqa: F401

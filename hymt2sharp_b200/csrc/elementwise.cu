@@ -228,3 +228,87 @@ HYMT2_API int hymt2_tanh(float* x, long total, cudaStream_t stream) {
     launch_pdl(tanh_kernel, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, x, (size_t)total);
     return hymt2_check_launch("tanh");
 }
+
+// A gated feed-forward's activation with clamps, on a [rows, 2 * width] input whose rows hold the gate half, then the up half:
+//     g = min(gate + bias_g, limit);  u = clamp(up + bias_u, -limit, limit);  out = g * sigmoid(alpha * g) * (u + 1)
+// (bias [2 * width] float32 or null).  The sums and the activation are float32.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, const float* __restrict__ bias, int width,
+                                   size_t total, float limit, float alpha) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t r = i / width;
+    const int c = (int)(i - r * width);
+    float g = to_float(gate_up[r * 2 * width + c]), u = to_float(gate_up[r * 2 * width + width + c]);
+    if (bias) { g += bias[c]; u += bias[width + c]; }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
+HYMT2_API int hymt2_clamped_glu(void* out, const void* gate_up, int dtype, const float* bias, int rows, int width, float limit, float alpha,
+                                cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && width > 0 && limit > 0.f, "clamped_glu: bad sizes rows=%d width=%d limit=%g", rows, width, (double)limit);
+    const size_t total = (size_t)rows * width;
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(clamped_glu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (T*)out,
+                                              (const T*)gate_up, bias, width, total, limit, alpha));
+    return hymt2_check_launch("clamped_glu");
+}
+
+// Rotary positions on rows of heads that lie side by side: y[t, :cols] = x[t, :cols] with the first rot_dims entries of each of
+// the first `heads` heads (d entries each) turned by angle = position * inv_freq[i]: pairing 0 pairs entry i with i + rot_dims/2,
+// pairing 1 entry 2i with 2i + 1; (a, b) -> (a cos - b sin, b cos + a sin).  Columns behind the heads are copied.  y may have
+// another type than x (float32: what enters a float32 recurrence is then never rounded), and may be x itself.
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(128)
+rotate_heads_kernel(TY* __restrict__ y, long ldy, const TX* __restrict__ x, long ldx, const int* __restrict__ token_pos,
+                    const float* __restrict__ inv_freq, int heads, int d, int rot_dims, int pairing, int cols) {
+    extern __shared__ float rot_cs[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, half = rot_dims / 2;
+    const int pos = token_pos[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, c;
+        sincosf((float)pos * inv_freq[i], &sn, &c);
+        rot_cs[2 * i] = c;
+        rot_cs[2 * i + 1] = sn;
+    }
+    __syncthreads();
+    const TX* src = x + (size_t)t * ldx;
+    TY* dst = y + (size_t)t * ldy;
+    const int per = half + (d - rot_dims);
+    for (int item = threadIdx.x; item < heads * per; item += blockDim.x) {
+        const int h = item / per, i = item - h * per;
+        const TX* s = src + (size_t)h * d;
+        TY* o = dst + (size_t)h * d;
+        if (i < half) {
+            const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+            const float a = to_float(s[ia]), b = to_float(s[ib]);
+            o[ia] = from_float<TY>(a * rot_cs[2 * i] - b * rot_cs[2 * i + 1]);
+            o[ib] = from_float<TY>(b * rot_cs[2 * i] + a * rot_cs[2 * i + 1]);
+        } else {
+            const int e = rot_dims + (i - half);
+            o[e] = from_float<TY>(to_float(s[e]));
+        }
+    }
+    if ((const void*)src != (const void*)dst || sizeof(TX) != sizeof(TY))
+        for (int c = heads * d + threadIdx.x; c < cols; c += blockDim.x) dst[c] = from_float<TY>(to_float(src[c]));
+}
+
+HYMT2_API int hymt2_rotate_heads(void* y, int y_dtype, long ldy, const void* x, int x_dtype, long ldx, const int* token_pos,
+                                 const float* inv_freq, int tokens, int heads, int d, int rot_dims, int pairing, int cols,
+                                 cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && heads >= 0 && d > 0 && cols >= heads * d, "rotate_heads: bad sizes");
+    HYMT2_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || inv_freq != nullptr),
+                  "rotate_heads: %d rotated entries of %d", rot_dims, d);
+    const size_t smem = sizeof(float) * (size_t)(rot_dims + 2);
+    HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(y_dtype, TY,
+        (launch_pdl(rotate_heads_kernel<TX, TY>, dim3(tokens), dim3(128), smem, stream, (TY*)y, ldy, (const TX*)x, ldx, token_pos, inv_freq,
+                    heads, d, rot_dims, pairing, cols))));
+    return hymt2_check_launch("rotate_heads");
+}

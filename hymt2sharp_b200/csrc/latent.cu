@@ -57,10 +57,11 @@ latent_prep_kernel(LatentPrepParams p) {
     // the latent vector's sum of squares (block_sum synchronises, which also publishes cs)
     const T* lat = row + p.q_cols;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
-        const float v = to_float(lat[i]);
-        ss = fmaf(v, v, ss);
-    }
+    if (p.cache || p.rows_out)      // (a projection without a compressed row of its own is never read behind its queries)
+        for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
+            const float v = to_float(lat[i]);
+            ss = fmaf(v, v, ss);
+        }
     ss = block_sum(ss, scratch);
     const int dl = p.rank + p.rot;
     T* dst = nullptr;    // the token's cache row

@@ -1,0 +1,161 @@
+// Layer norm with a gain and no bias, row by row, all in float32:
+//     y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * gain
+// (the variance is the mean of the squared deviations, taken in a pass of its own after the mean), in the forms that a
+// block with norms before AND after its sublayers needs: stored (optionally of gathered rows, optionally scaled), added
+// into float32 rows, and "added, then the next norm of the new rows" in one launch.  And the sum of several branches, each
+// divided by its own root mean square and multiplied by its own gain: out = sum_b scale_b * x_b / sqrt(mean(x_b^2) + eps) * gain_b.
+// One block per row; a row is read from global memory in every pass (it stays in L1/L2 between them).
+#include "common.cuh"
+
+namespace {
+
+template <typename TX>
+__device__ __forceinline__ void row_moments(const TX* __restrict__ src, int dim, float* scratch, float& mean, float& var) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) s += to_float(src[i]);
+    mean = block_sum(s, scratch) / (float)dim;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float d = to_float(src[i]) - mean;
+        q = fmaf(d, d, q);
+    }
+    var = block_sum(q, scratch) / (float)dim;
+}
+
+template <typename TX, typename TW, typename TY, bool ADD>
+__global__ void layernorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
+                                 const int* __restrict__ rows_index, int dim, float eps, float out_scale) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim;
+    float mean, var;
+    row_moments(src, dim, scratch, mean, var);
+    const float scale = 1.0f / sqrtf(var + eps);
+    TY* dst = y + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = (to_float(src[i]) - mean) * scale * to_float(gain[i]);
+        if (out_scale != 1.0f) v *= out_scale;
+        if constexpr (ADD) dst[i] = from_float<TY>(to_float(dst[i]) + v);
+        else dst[i] = from_float<TY>(v);
+    }
+}
+
+// y (float32) += norm_a(x); then h = norm_b(y) of the new y (gain_b null: h = the new y itself in h's type).
+template <typename TW, typename TH>
+__global__ void layernorm_add_norm_kernel(float* __restrict__ y, const float* __restrict__ x, const TW* __restrict__ gain_a,
+                                          TH* __restrict__ h, const TW* __restrict__ gain_b, int dim, float eps_a, float eps_b) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t off = (size_t)blockIdx.x * dim;
+    const float* src = x + off;
+    float* res = y + off;
+    TH* dst = h + off;
+    float mean, var;
+    row_moments(src, dim, scratch, mean, var);
+    const float scale_a = 1.0f / sqrtf(var + eps_a);
+    float s = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {   // a thread meets the same entries in every loop
+        const float v = res[i] + (src[i] - mean) * scale_a * to_float(gain_a[i]);
+        res[i] = v;
+        s += v;
+    }
+    if (gain_b == nullptr) {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = from_float<TH>(res[i]);
+        return;
+    }
+    const float mean_b = block_sum(s, scratch) / (float)dim;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float d = res[i] - mean_b;
+        q = fmaf(d, d, q);
+    }
+    const float scale_b = 1.0f / sqrtf(block_sum(q, scratch) / (float)dim + eps_b);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = from_float<TH>((res[i] - mean_b) * scale_b * to_float(gain_b[i]));
+}
+
+constexpr int MAX_NORMED_BRANCHES = 4;
+struct BranchSumParams {
+    const float* x[MAX_NORMED_BRANCHES];
+    const void* gain[MAX_NORMED_BRANCHES];
+    float scale[MAX_NORMED_BRANCHES];
+    float* out;
+    int count, dim;
+    float eps;
+};
+
+template <typename TW>
+__global__ void rmsnorm_sum_kernel(BranchSumParams p) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t off = (size_t)blockIdx.x * p.dim;
+    float r[MAX_NORMED_BRANCHES];
+#pragma unroll
+    for (int b = 0; b < MAX_NORMED_BRANCHES; b++) {
+        r[b] = 0.f;
+        if (b < p.count) {
+            const float* src = p.x[b] + off;
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < p.dim; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+            r[b] = p.scale[b] / sqrtf(block_sum(ss, scratch) / (float)p.dim + p.eps);
+        }
+    }
+    for (int i = threadIdx.x; i < p.dim; i += blockDim.x) {
+        float v = 0.f;
+#pragma unroll
+        for (int b = 0; b < MAX_NORMED_BRANCHES; b++)
+            if (b < p.count) v += p.x[b][off + i] * r[b] * to_float(((const TW*)p.gain[b])[i]);
+        p.out[off + i] = v;
+    }
+}
+
+inline int norm_threads(int dim) { return dim >= 2048 ? 256 : (dim >= 256 ? 128 : (dim >= 64 ? 64 : 32)); }
+
+}  // namespace
+
+HYMT2_API int hymt2_layernorm(void* y, int y_dtype, const void* x, int x_dtype, const void* gain, int gain_dtype, const int* rows_index,
+                              int rows, int dim, float eps, float out_scale, int add, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
+    HYMT2_REQUIRE(!add || y_dtype == HYMT2_F32, "layernorm: adding into the output needs float32 rows");
+    const int threads = norm_threads(dim);
+    HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
+        if (add) {
+            launch_pdl(layernorm_kernel<TX, TW, float, true>, dim3(rows), dim3(threads), 0, stream, (float*)y, (const TX*)x, (const TW*)gain,
+                       rows_index, dim, eps, out_scale);
+        } else {
+            HYMT2_DISPATCH_DTYPE(y_dtype, TY, (launch_pdl(layernorm_kernel<TX, TW, TY, false>, dim3(rows), dim3(threads), 0, stream, (TY*)y,
+                                                          (const TX*)x, (const TW*)gain, rows_index, dim, eps, out_scale)));
+        }
+    }));
+    return hymt2_check_launch("layernorm");
+}
+
+HYMT2_API int hymt2_layernorm_add_norm(float* y, const float* x, const void* gain_a, void* h, int h_dtype, const void* gain_b, int gain_dtype,
+                                       int rows, int dim, float eps_a, float eps_b, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
+    HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
+        (launch_pdl(layernorm_add_norm_kernel<TW, TH>, dim3(rows), dim3(norm_threads(dim)), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
+                    (const TW*)gain_b, dim, eps_a, eps_b))));
+    return hymt2_check_launch("layernorm_add_norm");
+}
+
+HYMT2_API int hymt2_rmsnorm_sum(float* out, const float* const* x, const void* const* gain, const float* scale, int count, int gain_dtype,
+                                int rows, int dim, float eps, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && dim > 0 && count >= 1 && count <= MAX_NORMED_BRANCHES, "rmsnorm_sum: bad sizes rows=%d dim=%d branches=%d",
+                  rows, dim, count);
+    BranchSumParams p;
+    for (int b = 0; b < MAX_NORMED_BRANCHES; b++) {
+        p.x[b] = b < count ? x[b] : nullptr;
+        p.gain[b] = b < count ? gain[b] : nullptr;
+        p.scale[b] = b < count ? scale[b] : 0.f;
+    }
+    p.out = out; p.count = count; p.dim = dim; p.eps = eps;
+    HYMT2_DISPATCH_DTYPE(gain_dtype, TW, launch_pdl(rmsnorm_sum_kernel<TW>, dim3(rows), dim3(norm_threads(dim)), 0, stream, p));
+    return hymt2_check_launch("rmsnorm_sum");
+}

@@ -444,7 +444,7 @@ scan_carry_kernel(ScanParams p) {
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, long ldg, const float* __restrict__ weight,
-                      long items, int heads, int dv, float eps) {
+                      long items, int heads, int dv, float eps, int gate_sigmoid) {
     pdl_wait();
     pdl_launch_dependents();
     const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -462,7 +462,7 @@ head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T*
         if (weight) y *= weight[(size_t)head * dv + c];
         if (gate) {
             const float g = to_float(gate[(size_t)t * ldg + (size_t)head * dv + c]);
-            y *= g / (1.0f + expf(-g));
+            y *= (gate_sigmoid ? 1.0f : g) / (1.0f + expf(-g));
         }
         out[(size_t)item * dv + c] = from_float<T>(y);
     }
@@ -473,7 +473,7 @@ head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T*
 template <typename T, int P>
 __global__ void __launch_bounds__(128)
 head_norm_gate_wide_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, long ldg,
-                           const float* __restrict__ weight, long items, int heads, int dv, float eps) {
+                           const float* __restrict__ weight, long items, int heads, int dv, float eps, int gate_sigmoid) {
     pdl_wait();
     pdl_launch_dependents();
     const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -510,7 +510,7 @@ head_norm_gate_wide_kernel(T* __restrict__ out, const float* __restrict__ o, con
                 if (weight) v *= w.v[e];
                 if (gate) {
                     const float gv = to_float(g[p].v[e]);
-                    v *= gv / (1.0f + expf(-gv));
+                    v *= (gate_sigmoid ? 1.0f : gv) / (1.0f + expf(-gv));
                 }
                 y.v[e] = from_float<T>(v);
             }
@@ -621,7 +621,7 @@ HYMT2_API int hymt2_linear_scan(float* out, const void* q, const void* k, const 
 }
 
 HYMT2_API int hymt2_head_norm_gate(void* out, const float* o, const void* gate, long ldg, int dtype, const float* weight, int tokens,
-                                   int heads, int dv, float eps, cudaStream_t stream) {
+                                   int heads, int dv, float eps, int gate_sigmoid, cudaStream_t stream) {
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && heads > 0 && dv > 0, "head_norm_gate: bad sizes");
     const long items = (long)tokens * heads;
@@ -631,13 +631,13 @@ HYMT2_API int hymt2_head_norm_gate(void* out, const float* o, const void* gate, 
         const bool wide = dv % 4 == 0 && dv <= 512 && (uintptr_t)o % 16 == 0 && (uintptr_t)out % (4 * sizeof(T)) == 0 &&
                           (!gate || ((uintptr_t)gate % (4 * sizeof(T)) == 0 && ldg % 4 == 0)) && (!weight || (uintptr_t)weight % 16 == 0);
         if (wide && dv <= 128)
-            launch_pdl(head_norm_gate_wide_kernel<T, 1>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+            launch_pdl(head_norm_gate_wide_kernel<T, 1>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps, gate_sigmoid);
         else if (wide && dv <= 256)
-            launch_pdl(head_norm_gate_wide_kernel<T, 2>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+            launch_pdl(head_norm_gate_wide_kernel<T, 2>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps, gate_sigmoid);
         else if (wide)
-            launch_pdl(head_norm_gate_wide_kernel<T, 4>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+            launch_pdl(head_norm_gate_wide_kernel<T, 4>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps, gate_sigmoid);
         else
-            launch_pdl(head_norm_gate_kernel<T>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps);
+            launch_pdl(head_norm_gate_kernel<T>, grid, dim3(128), 0, stream, (T*)out, o, (const T*)gate, ldg, weight, items, heads, dv, eps, gate_sigmoid);
     });
     return hymt2_check_launch("head_norm_gate");
 }

@@ -22,7 +22,8 @@ struct ConvParams {
     int channels, taps, ldx, ldo, add_input;
 };
 
-// out_t = (add_input ? x_t : 0) + bias + sum_j w[:, j] * x_(t - taps + 1 + j), zeros before the sequence's start.
+// out_t = act((add_input & 1 ? x_t : 0) + bias + sum_j w[:, j] * x_(t - taps + 1 + j)), zeros before the sequence's start;
+// act is SiLU with bit 1 of add_input, else nothing.
 // One thread owns a channel over a chunk of a sequence's new tokens and slides a window of registers over it.  The
 // thread of the first chunk is the only one that reads the state (for the inputs before this step) and, once it has,
 // writes the new one: the last taps - 1 inputs of (old state, new tokens).
@@ -105,7 +106,8 @@ causal_conv_kernel(ConvParams p) {
             for (int j = 0; j < MAXT; j++)
                 if (j == hist) a = fmaf(w[j][k], cur[k], a);
             a += bias[k];
-            if (p.add_input) a += cur[k];
+            if (p.add_input & 1) a += cur[k];
+            if (p.add_input & 2) a = a / (1.0f + expf(-a));   // SiLU of the filter's output
             acc[k] = a;
         }
         store_chan<T, V>(out + (size_t)i * p.ldo, acc);

@@ -839,9 +839,9 @@ def _rows_view(t: torch.Tensor, name: str, dtype=None) -> int:
 
 def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                 state_offset: int, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
-                max_new_tokens: int, add_input: bool) -> None:
-    """Causal convolution over time on each channel: out_t = (x_t if add_input) + bias + sum_j w[:, j] x_(t - taps + 1 + j),
-    zeros before a sequence's start.  `state` is the cache's byte matrix [slots, bytes]; from byte `state_offset` of a
+                max_new_tokens: int, add_input: bool, silu: bool = False) -> None:
+    """Causal convolution over time on each channel: out_t = act((x_t if add_input) + bias + sum_j w[:, j] x_(t - taps + 1 + j)),
+    zeros before a sequence's start; act is SiLU if `silu`, else nothing.  `state` is the cache's byte matrix [slots, bytes]; from byte `state_offset` of a
     slot's row lie float32 [taps - 1, channels], the sequence's last inputs, which the kernel reads and renews."""
     ldx, ldo = _rows_view(x, "x"), _rows_view(out, "out", x.dtype)
     T, C = x.shape
@@ -856,7 +856,7 @@ def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: torch
     _check(_lib().hymt2_causal_conv(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w), _ptr(bias), _ptr(state),
                                     c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens),
                                     c_int(batch), c_int(max_new_tokens), c_int(C), c_int(taps), c_int(ldx), c_int(ldo),
-                                    c_int(1 if add_input else 0), _stream()), "causal_conv")
+                                    c_int((1 if add_input else 0) | (2 if silu else 0)), _stream()), "causal_conv")
 
 
 def rglru_scan(out: torch.Tensor, gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, br: torch.Tensor, bi: torch.Tensor,
@@ -943,7 +943,8 @@ def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor | None, cac
     the normed latent vector and the rotated shared key part go to the token's cache row [rank + rot]; every head's
     rotated query part goes to q_out[t, h, rank : rank + rot].  Pairs (2i, 2i+1) turn by position * inv_freq[i], cosine
     and sine times `amplitude`.  cache_plane None: nothing is cached.  q_out None: the rotated query parts are written
-    back into proj, in place.  rows_out [T, rank + rot]: the cache rows once more, side by side for all tokens."""
+    back into proj, in place.  rows_out [T, rank + rot]: the cache rows once more, side by side for all tokens.  With neither a
+    cache plane nor rows_out the projection need not hold a compressed row at all (only the queries are read)."""
     ldp = _rows_view(proj, "proj")
     T = proj.shape[0]
     dl = rank + rot
@@ -951,7 +952,9 @@ def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor | None, cac
         _need(q_out, "q_out", proj.dtype, 2)
     if rows_out is not None:
         _need(rows_out, "rows_out", proj.dtype, 2)
-    if proj.shape[1] < q_cols + dl or q_cols != heads * (dim + rot) or (q_out is not None and q_out.shape != (T, heads * dl)) \
+    # a run without a compressed row of its own (it reads another run's cache) brings the queries alone
+    rowless = cache_plane is None and rows_out is None
+    if proj.shape[1] < q_cols + (0 if rowless else dl) or q_cols != heads * (dim + rot) or (q_out is not None and q_out.shape != (T, heads * dl)) \
             or (rows_out is not None and rows_out.shape != (T, dl)):
         raise KernelError(f"latent_prep: shapes proj {tuple(proj.shape)} do not fit {heads} heads of {dim} + {rot} and a row of {dl}")
     if cache_plane is not None:
@@ -1520,8 +1523,9 @@ def linear_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Te
 
 
 def head_norm_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor | None, heads: int, dv: int,
-                   eps: float) -> None:
-    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight[h, :] * silu(gate[t, h, :]); weight and gate are optional,
+                   eps: float, gate_act: str = "silu") -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight[h, :] * act(gate[t, h, :]); act is SiLU or, with
+    gate_act "sigmoid", the sigmoid; weight and gate are optional,
     o is float32, gate (rows may be columns of a wider matrix) and out have the compute type."""
     _need(out, "out", None, 2); _need(o, "o", torch.float32, 2)
     T = out.shape[0]
@@ -1534,7 +1538,7 @@ def head_norm_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor | None
     if out.shape != (T, heads * dv) or o.shape != out.shape:
         raise KernelError(f"head_norm_gate: shapes out {tuple(out.shape)} o {tuple(o.shape)}")
     _check(_lib().hymt2_head_norm_gate(_ptr(out), _ptr(o), _ptr(gate), c_long(ldg), c_int(dtype_code(out.dtype)), _ptr(weight), c_int(T),
-                                       c_int(heads), c_int(dv), c_float(eps), _stream()), "head_norm_gate")
+                                       c_int(heads), c_int(dv), c_float(eps), c_int(1 if gate_act == "sigmoid" else 0), _stream()), "head_norm_gate")
 
 
 def token_shift(mixes: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_offset: int, token_seq: torch.Tensor,
@@ -1574,3 +1578,187 @@ def tanh_(x: torch.Tensor) -> None:
     """In place on float32 values."""
     _need(x, "x", torch.float32)
     _check(_lib().hymt2_tanh(_ptr(x), c_long(x.numel()), _stream()), "tanh")
+
+
+# -- layer norm, and branches that are normed before they are added ------------------------------------------------------------------
+def layernorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, rows_index: torch.Tensor | None = None,
+              scale: float = 1.0, add: bool = False) -> None:
+    """out[r] = (x[r'] - mean) / sqrt(mean((x[r'] - mean)^2) + eps) * gain * scale, r' = rows_index[r] or r; `add`: added into out
+    (float32) instead of stored."""
+    _need(out, "out", None, 2); _need(x, "x", None, 2); _need(gain, "gain", None, 1)
+    rows, dim = out.shape
+    if x.shape[1] != dim or gain.shape[0] != dim or (rows_index is None and x.shape[0] != rows):
+        raise KernelError(f"layernorm: shapes out {tuple(out.shape)} x {tuple(x.shape)} gain {tuple(gain.shape)}")
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32, 1)
+        if rows_index.shape[0] < rows:
+            raise KernelError("layernorm: fewer row numbers than rows")
+    _check(_lib().hymt2_layernorm(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(gain),
+                                  c_int(dtype_code(gain.dtype)), _ptr(rows_index), c_int(rows), c_int(dim), c_float(eps), c_float(scale),
+                                  c_int(1 if add else 0), _stream()), "layernorm")
+
+
+def layernorm_add_norm(residual: torch.Tensor, x: torch.Tensor, gain_a: torch.Tensor, eps_a: float, out: torch.Tensor,
+                       gain_b: torch.Tensor | None, eps_b: float) -> None:
+    """residual (float32) += layernorm_a(x); out = layernorm_b(residual) of the new rows, or (gain_b None) the new rows themselves
+    in out's type."""
+    _need(residual, "residual", torch.float32, 2); _need(x, "x", torch.float32, 2); _need(out, "out", None, 2); _need(gain_a, "gain_a", None, 1)
+    rows, dim = residual.shape
+    if x.shape != residual.shape or out.shape != residual.shape or gain_a.shape[0] != dim:
+        raise KernelError(f"layernorm_add_norm: shapes residual {tuple(residual.shape)} x {tuple(x.shape)} out {tuple(out.shape)}")
+    if gain_b is not None:
+        _need(gain_b, "gain_b", gain_a.dtype, 1)
+        if gain_b.shape[0] != dim:
+            raise KernelError("layernorm_add_norm: the second gain's width differs")
+    _check(_lib().hymt2_layernorm_add_norm(_ptr(residual), _ptr(x), _ptr(gain_a), _ptr(out), c_int(dtype_code(out.dtype)), _ptr(gain_b),
+                                           c_int(dtype_code(gain_a.dtype)), c_int(rows), c_int(dim), c_float(eps_a), c_float(eps_b),
+                                           _stream()), "layernorm_add_norm")
+
+
+MAX_NORMED_BRANCHES = 4
+
+
+def rmsnorm_sum(out: torch.Tensor, branches: list, gains: list, scales: list, eps: float) -> None:
+    """out (float32) = sum_b scales[b] * branches[b] / sqrt(mean(branches[b]^2) + eps) * gains[b], row by row."""
+    _need(out, "out", torch.float32, 2)
+    n = len(branches)
+    if not (1 <= n <= MAX_NORMED_BRANCHES) or len(gains) != n or len(scales) != n:
+        raise KernelError(f"rmsnorm_sum: {n} branches (1 to {MAX_NORMED_BRANCHES}), a gain and a scale each")
+    for x, g in zip(branches, gains):
+        _need(x, "branch", torch.float32, 2); _need(g, "gain", gains[0].dtype, 1)
+        if x.shape != out.shape or g.shape[0] != out.shape[1]:
+            raise KernelError(f"rmsnorm_sum: a branch is {tuple(x.shape)} with a gain of {tuple(g.shape)}, out is {tuple(out.shape)}")
+    xs = (c_void_p * n)(*[x.data_ptr() for x in branches])
+    gs = (c_void_p * n)(*[g.data_ptr() for g in gains])
+    sc = (c_float * n)(*[float(s) for s in scales])
+    _check(_lib().hymt2_rmsnorm_sum(_ptr(out), xs, gs, sc, c_int(n), c_int(dtype_code(gains[0].dtype)), c_int(out.shape[0]),
+                                    c_int(out.shape[1]), c_float(eps), _stream()), "rmsnorm_sum")
+
+
+# -- clamped gated activation; rotary positions on heads side by side ------------------------------------------------------------------
+def clamped_glu(out: torch.Tensor, gate_up: torch.Tensor, bias: torch.Tensor | None, limit: float, alpha: float) -> None:
+    """g = min(gate + bias_g, limit); u = clamp(up + bias_u, -limit, limit); out = g * sigmoid(alpha * g) * (u + 1), for rows
+    [gate half | up half] of gate_up [rows, 2 * width] and bias [2 * width] float32 (or None)."""
+    _need(out, "out", None, 2); _need(gate_up, "gate_up", out.dtype, 2)
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width):
+        raise KernelError(f"clamped_glu: shapes out {tuple(out.shape)} gate_up {tuple(gate_up.shape)}")
+    _f32(bias, "bias", 2 * width)
+    _check(_lib().hymt2_clamped_glu(_ptr(out), _ptr(gate_up), c_int(dtype_code(out.dtype)), _ptr(bias), c_int(rows), c_int(width),
+                                    c_float(limit), c_float(alpha), _stream()), "clamped_glu")
+
+
+def rotate_heads(out: torch.Tensor, x: torch.Tensor, token_pos: torch.Tensor, inv_freq: torch.Tensor | None, heads: int, d: int,
+                 rot_dims: int, pairing: str) -> None:
+    """out[t] = x[t] with the first rot_dims entries of each of the first `heads` heads (d entries each, side by side from column
+    0) turned by position * inv_freq[i]; pairing "half": entries (i, i + rot_dims/2), "interleaved": (2i, 2i + 1).  The columns
+    behind the heads are copied.  out may have another type than x (rows of both may be columns of wider matrices)."""
+    ldx, ldy = _rows_view(x, "x"), _rows_view(out, "out")
+    if out.shape != x.shape or x.shape[1] < heads * d or pairing not in ("half", "interleaved"):
+        raise KernelError(f"rotate_heads: shapes out {tuple(out.shape)} x {tuple(x.shape)} for {heads} heads of {d}, pairing {pairing}")
+    _need(token_pos, "token_pos", torch.int32, 1); _f32(inv_freq, "inv_freq", rot_dims // 2)
+    _check(_lib().hymt2_rotate_heads(_ptr(out), c_int(dtype_code(out.dtype)), c_long(ldy), _ptr(x), c_int(dtype_code(x.dtype)), c_long(ldx),
+                                     _ptr(token_pos), _ptr(inv_freq), c_int(x.shape[0]), c_int(heads), c_int(d), c_int(rot_dims),
+                                     c_int(1 if pairing == "interleaved" else 0), c_int(x.shape[1]), _stream()), "rotate_heads")
+
+
+# -- attention whose heads talk ------------------------------------------------------------------------------------------------
+MASKS = {None: 0, "chunk": 1, "window": 2}
+
+
+def talk_prep(x: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None, block_table: torch.Tensor,
+              block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None,
+              rot_dims: int, heads: int, kv_heads: int, d: int) -> None:
+    """x [T, heads * d | kv_heads * d] (q, then k; rows may be columns of a wider matrix): q rotated in (2i, 2i+1) pairs goes to
+    q_out [T, heads * d]; k rotated goes to the key plane and k as it is to the value plane of the token's cache row."""
+    ldx = _rows_view(x, "x")
+    T = x.shape[0]
+    _need(q_out, "q_out", x.dtype, 2)
+    if x.shape[1] != (heads + kv_heads) * d or q_out.shape != (T, heads * d):
+        raise KernelError(f"talk_prep: shapes x {tuple(x.shape)} q_out {tuple(q_out.shape)}")
+    if k_plane is not None:
+        _need(k_plane, "k_plane", x.dtype, 4); _need(v_plane, "v_plane", x.dtype, 4)
+        if k_plane.shape[1:] != (kv_heads, block_tokens, d) or v_plane.shape != k_plane.shape:
+            raise KernelError(f"talk_prep: cache planes {tuple(k_plane.shape)} {tuple(v_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
+        _need(t, n, torch.int32, 1)
+    _f32(inv_freq, "inv_freq", rot_dims // 2)
+    _check(_lib().hymt2_talk_prep(_ptr(x), c_long(ldx), c_int(dtype_code(x.dtype)), _ptr(q_out), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
+                                  c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq), _ptr(token_pos), _ptr(slot_ids),
+                                  _ptr(inv_freq), c_int(rot_dims), c_int(T), c_int(heads), c_int(kv_heads), c_int(d), _stream()), "talk_prep")
+
+
+def talking_attention(out: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | None, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                      block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+                      max_new_tokens: int, heads: int, kv_heads: int, d: int, scale: float, talk: torch.Tensor, temp: torch.Tensor,
+                      sink: torch.Tensor | None, mask: str | None, mask_size: int) -> None:
+    """Attention of the new tokens over the paged cache with the heads' scores mixed before the softmax:
+    s_h = sum_g talk[h, g] * temp[g] * scale * (q_g . k_g); a sink per head in the denominator (or None); mask None (causal),
+    "chunk" (only keys of the query's own chunk of mask_size positions) or "window" (the last mask_size); the output times
+    sigmoid(gate) entry by entry where a gate [T, heads * d] is given.  float32 scores and softmax."""
+    _need(out, "out", None, 2); _need(q, "q", out.dtype, 2); _need(k_plane, "k_plane", out.dtype, 4); _need(v_plane, "v_plane", out.dtype, 4)
+    T = out.shape[0]
+    if out.shape[1] != heads * d or q.shape != out.shape or k_plane.shape[1] != kv_heads or k_plane.shape[3] != d or v_plane.shape != k_plane.shape:
+        raise KernelError(f"talking_attention: shapes out {tuple(out.shape)} q {tuple(q.shape)} keys {tuple(k_plane.shape)} values {tuple(v_plane.shape)}")
+    ldg = 0
+    if gate is not None:
+        ldg = _rows_view(gate, "gate", out.dtype)
+        if gate.shape != out.shape:
+            raise KernelError("talking_attention: the gate's shape differs")
+    _f32(talk, "talk", heads * heads); _f32(temp, "temp", heads); _f32(sink, "sink", heads)
+    if mask not in MASKS:
+        raise KernelError(f"talking_attention: mask '{mask}' (known: None, 'chunk', 'window')")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_talking_attention(_ptr(out), _ptr(q), _ptr(gate), c_long(ldg), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(out.dtype)),
+                                          _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens),
+                                          _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(max_new_tokens), c_int(heads), c_int(kv_heads),
+                                          c_int(d), c_float(scale), _ptr(talk), _ptr(temp), _ptr(sink), c_int(MASKS[mask]),
+                                          c_int(mask_size), _stream()), "talking_attention")
+
+
+# -- the gated delta rule ----------------------------------------------------------------------------------------------------------
+def delta_scan_max_dk() -> int:
+    return int(_lib().hymt2_delta_scan_max_dk())
+
+
+def delta_prep(qk: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, heads: int, kv_heads: int, dk: int, q_scale: float, unit_eps: float) -> None:
+    """What enters the delta rule, in float32: qn, kn [T, kv_heads * dk] = q, k (columns of qk, q first) as unit vectors
+    x / sqrt(sum(x^2) + unit_eps), q times q_scale; decay [T, heads * dk] in place x -> exp(-exp(a_log[h]) * softplus(x + dt_bias));
+    beta [T, heads] in place x -> sigmoid(x)."""
+    ldqk = _rows_view(qk, "qk")
+    T = qk.shape[0]
+    _need(qn, "qn", torch.float32, 2); _need(kn, "kn", torch.float32, 2); _need(decay, "decay", torch.float32, 2)
+    ldb = _rows_view(beta, "beta", torch.float32)
+    if qk.shape[1] != 2 * kv_heads * dk or qn.shape != (T, kv_heads * dk) or kn.shape != qn.shape or decay.shape != (T, heads * dk) \
+            or beta.shape != (T, heads):
+        raise KernelError(f"delta_prep: shapes qk {tuple(qk.shape)} qn {tuple(qn.shape)} decay {tuple(decay.shape)} beta {tuple(beta.shape)}")
+    _f32(dt_bias, "dt_bias", heads * dk); _f32(a_log, "a_log", heads)
+    _check(_lib().hymt2_delta_prep(_ptr(qk), c_long(ldqk), c_int(dtype_code(qk.dtype)), _ptr(qn), _ptr(kn), _ptr(decay), _ptr(beta), c_long(ldb),
+                                   _ptr(dt_bias), _ptr(a_log), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_float(q_scale),
+                                   c_float(unit_eps), _stream()), "delta_prep")
+
+
+def delta_scan(out: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, v: torch.Tensor,
+               state: torch.Tensor, state_offset: int, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+               heads: int, kv_heads: int, dk: int, dv: int) -> None:
+    """Per (sequence, head), S [dk, dv] float32 at byte `state_offset` of the state row as [heads, dk, dv] (ignored by a sequence that
+    starts at position 0): S = diag(decay_t) S; u = beta_t (v_t - S^T k_t); S += k_t u^T; out_t = S^T q_t.  qn, kn, decay, beta as
+    delta_prep leaves them; v [T, heads * dv] in the compute type (rows may be columns of a wider matrix); out float32."""
+    _need(out, "out", torch.float32, 2); _need(qn, "qn", torch.float32, 2); _need(kn, "kn", torch.float32, 2); _need(decay, "decay", torch.float32, 2)
+    T = out.shape[0]
+    ldv, ldb = _rows_view(v, "v"), _rows_view(beta, "beta", torch.float32)
+    if out.shape[1] != heads * dv or qn.shape != (T, kv_heads * dk) or kn.shape != qn.shape or decay.shape != (T, heads * dk) \
+            or beta.shape != (T, heads) or v.shape != (T, heads * dv):
+        raise KernelError(f"delta_scan: shapes out {tuple(out.shape)} qn {tuple(qn.shape)} decay {tuple(decay.shape)} v {tuple(v.shape)}")
+    if state.dtype != torch.uint8 or state.dim() != 2 or state_offset % 4 or state_offset + 4 * heads * dk * dv > state.shape[1]:
+        raise KernelError("delta_scan: the state rows are too short")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(decay), _ptr(beta), c_long(ldb), _ptr(v), c_long(ldv),
+                                   c_int(dtype_code(v.dtype)), _ptr(state), c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens),
+                                   _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+                                   _stream()), "delta_scan")

@@ -79,14 +79,27 @@ class SandwichBlock:
     The norms in FRONT are optional (`norm1` / `norm2` None): such a sublayer reads the residual rows themselves, and the norm
     is on its output only, x += norm1b(mixer(x)).  In an engine whose compute type is not float32 the rows are rounded once;
     the kernel of the norm behind a sublayer writes that rounding beside the new residual, also for the block that runs next
-    (left in `ctx.shared["residual_rows"]`)."""
+    (left in `ctx.shared["residual_rows"]`).
 
-    def __init__(self, norm1: PartSpec | None, mixer: PartSpec, norm1_after: PartSpec, norm2: PartSpec | None = None,
+    Several mixers side by side (`mixers` = [(PartSpec, gain tensor name, scale), ...] in place of `mixer`): all read the same h,
+    each has its own cache plane and state (cache_needs() / state_bytes() list them first, in order), and the first sublayer's
+    output is sum_i scale_i * y_i / sqrt(mean(y_i^2) + mixers_eps) * gain_i: every mixer's output is divided by its own root
+    mean square over the model width and multiplied by its own stored gain before the sum (one kernel)."""
+
+    def __init__(self, norm1: PartSpec | None, mixer: PartSpec | None, norm1_after: PartSpec, norm2: PartSpec | None = None,
                  feed_forward: PartSpec | None = None, norm2_after: PartSpec | None = None, conv1: dict | None = None,
-                 conv2: dict | None = None):
+                 conv2: dict | None = None, mixers: list | None = None, mixers_eps: float = 0.0):
         from .conv import ShortConv
+        if (mixer is None) == (not mixers):
+            raise ValueError("a block holds one mixer (`mixer`) or several side by side (`mixers`), not both and not neither")
+        if mixers and len(mixers) > ops.MAX_NORMED_BRANCHES:
+            raise ValueError(f"{len(mixers)} mixers side by side (at most {ops.MAX_NORMED_BRANCHES})")
         self.norm1 = build_part("norm", norm1) if norm1 is not None else None
-        self.mixer = build_part("mixer", mixer)
+        self.side = [build_part("mixer", m) for m, _, _ in mixers] if mixers else []
+        self.side_names = [name for _, name, _ in mixers] if mixers else []
+        self.side_scales = [float(sc) for _, _, sc in mixers] if mixers else []
+        self.side_eps, self.side_gains = float(mixers_eps), []
+        self.mixer = build_part("mixer", mixer) if mixer is not None else None
         self.norm1_after = build_part("norm", norm1_after)
         self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
         self.norm2 = build_part("norm", norm2) if feed_forward is not None and norm2 is not None else None
@@ -95,38 +108,47 @@ class SandwichBlock:
         self.conv2 = ShortConv(add_input=True, **conv2) if conv2 is not None and feed_forward is not None else None
 
     def parts(self):
-        return tuple(p for p in (self.norm1, self.conv1, self.mixer, self.norm1_after, self.norm2, self.conv2,
+        return tuple(p for p in (self.norm1, self.conv1, self.mixer, *self.side, self.norm1_after, self.norm2, self.conv2,
                                  self.feed_forward, self.norm2_after) if p is not None)
 
     def _convs(self):
         return [c for c in (self.conv1, self.conv2) if c is not None]
 
+    def _mixers(self):
+        return [self.mixer] if self.mixer is not None else self.side
+
     def cache_needs(self) -> list:
-        return [self.mixer.cache_need()] + [None for _ in self._convs()]
+        return [m.cache_need() for m in self._mixers()] + [None for _ in self._convs()]
 
     def state_bytes(self) -> list:
-        return [int(self.mixer.state_bytes())] + [c.state_bytes() for c in self._convs()]
+        return [int(m.state_bytes()) for m in self._mixers()] + [c.state_bytes() for c in self._convs()]
 
     @property
     def graph_safe(self) -> bool:
         return all(getattr(p, "graph_safe", False) for p in self.parts())
 
     def tensors(self):
+        from ..weights.loader import TensorSpec
         t = {}
         for p in self.parts():
             t.update(p.tensors())
+        width = self.norm1_after.dim
+        for name in self.side_names:
+            t[name] = TensorSpec((width,), init="gain")
         return t
 
     def load(self, weights, device, dtype):
+        from .linear import compute_form
         for p in self.parts():
             p.load(weights, device, dtype)
+        self.side_gains = [compute_form(weights[name], device, dtype) for name in self.side_names]
 
     def first_norm(self):
         return None   # what reads the residual first here is followed by a convolution, which wants the plain rows
 
     def forward(self, residual, ctx, slots) -> None:
         import torch
-        conv_slots = list(slots[1:])
+        conv_slots = list(slots[len(self._mixers()):])
         ctx.weights_ahead = ctx.norm_ahead = None
         left = ctx.shared.pop("residual_rows", None)
         if self.norm1 is not None:
@@ -137,7 +159,15 @@ class SandwichBlock:
             h = self._rows(residual, ctx)
         if self.conv1 is not None:
             h = self.conv1.forward(h, ctx, conv_slots.pop(0))
-        if getattr(self.mixer, "can_store", False):
+        if self.side:
+            outs = []
+            for mixer, slot in zip(self.side, slots):
+                y = torch.empty_like(residual) if getattr(mixer, "can_store", False) else torch.zeros_like(residual)
+                mixer.forward(h, y, ctx, slot, **({"store": True} if getattr(mixer, "can_store", False) else {}))
+                outs.append(y)
+            branch = torch.empty_like(residual)
+            ops.rmsnorm_sum(branch, outs, self.side_gains, self.side_scales, self.side_eps)
+        elif getattr(self.mixer, "can_store", False):
             branch = torch.empty_like(residual)
             self.mixer.forward(h, branch, ctx, slots[0], store=True)
         else:

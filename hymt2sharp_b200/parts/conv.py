@@ -17,15 +17,22 @@ from ..weights.loader import TensorSpec
 class ShortConv:
     graph_safe = True
 
-    def __init__(self, channels: int, taps: int, weight: str, bias: str | None = None, add_input: bool = False):
+    def __init__(self, channels: int, taps: int, weight, bias: str | None = None, add_input: bool = False,
+                 activation: str | None = None):
         if taps < 1:
             raise ValueError(f"a convolution needs at least one tap, got {taps}")
-        self.channels, self.taps, self.add_input = int(channels), int(taps), bool(add_input)
-        self.weight_name, self.bias_name = weight, bias
+        if activation not in (None, "silu"):
+            raise ValueError(f"activation '{activation}' of a convolution: known are 'silu' and None")
+        self.channels, self.taps, self.add_input, self.activation = int(channels), int(taps), bool(add_input), activation
+        # `weight`: one tensor name, or [(name, channels), ...]: several filters side by side that run as one convolution
+        self.pieces = [(weight, self.channels)] if isinstance(weight, str) else [(n, int(c)) for n, c in weight]
+        if sum(c for _, c in self.pieces) != self.channels:
+            raise ValueError("the filters side by side do not add up to the convolution's channels")
+        self.weight_name, self.bias_name = self.pieces[0][0], bias
         self.w = self.b = None
 
     def tensors(self):
-        t = {self.weight_name: TensorSpec((self.channels, self.taps))}
+        t = {name: TensorSpec((c, self.taps)) for name, c in self.pieces}
         if self.bias_name is not None:
             t[self.bias_name] = TensorSpec((self.channels,))
         return t
@@ -35,12 +42,12 @@ class ShortConv:
 
     def load(self, weights, device, dtype):
         # the filter and its bias are used as float32 in both precisions (they are a few values per channel)
-        self.w = weights[self.weight_name].to(device).float().contiguous()
+        self.w = torch.cat([weights[name].to(device).float() for name, _ in self.pieces], dim=0).contiguous()
         self.b = weights[self.bias_name].to(device).float().contiguous() if self.bias_name is not None else None
 
     def forward(self, x: torch.Tensor, ctx, slot) -> torch.Tensor:
         """x [T, channels] (rows may be columns of a wider matrix); returns a new [T, channels] of x's type."""
         out = torch.empty((x.shape[0], self.channels), dtype=x.dtype, device=x.device)
         ops.causal_conv(out, x, self.w, self.b, ctx.cache.state, slot.state_offset, ctx.cu_seqlens, ctx.slot_ids,
-                        ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens, self.add_input)
+                        ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens, self.add_input, self.activation == "silu")
         return out

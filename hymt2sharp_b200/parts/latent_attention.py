@@ -15,6 +15,11 @@ the rotation are float32; the projections run in the engine's compute type.
 A prompt that starts at position 0 brings all of its keys along, and a head's own rows (dim + rot_dim, vdim) are several
 times narrower than the compressed row: there the bfloat16 engine rebuilds every head's keys and values with one product
 over all tokens and runs the attention per head, which is the same sums in another order (EXPAND_FROM_TOKENS).
+
+`own_kv` False: the layer has no down-projection and no latent norm; it attends over the compressed rows that another run
+cached (the model's order names it), with its own up-projections, queries, window and gate.  `cache_window`: the positions that
+the cache keeps for this plane when that is more than the layer's own window (readers of one plane may look back differently
+far; 0 with a window elsewhere means: keep everything).
 """
 from __future__ import annotations
 
@@ -38,13 +43,18 @@ class LatentAttention:
 
     def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
                  position: PartSpec | None, gate: str | None, q_proj: str, dkv_proj: str, dkv_norm: str, uk_proj: str,
-                 uv_proj: str, o_proj: str, g_proj: str | None = None, window: int | None = None):
+                 uv_proj: str, o_proj: str, g_proj: str | None = None, window: int | None = None, own_kv: bool = True,
+                 cache_window: int | None = None):
         if gate not in (None, "element", "head"):
             raise ValueError(f"output gate '{gate}': known are 'element' (one value per output entry), 'head' and None")
         if gate is not None and g_proj is None:
             raise ValueError("an output gate needs its projection's tensor name")
         self.hidden, self.heads, self.dim, self.rot, self.vdim, self.rank = hidden, heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.gate, self.window = float(scale), float(eps), gate, int(window or 0)
+        self.own_kv = bool(own_kv)
+        self.cache_window = self.window if cache_window is None else int(cache_window)
+        if self.cache_window and (not self.window or self.cache_window < self.window):
+            raise ValueError(f"a cache that keeps {self.cache_window} positions is too short for a window of {self.window or 'everything'}")
         self.names = dict(q=q_proj, dkv=dkv_proj, cn=dkv_norm, uk=uk_proj, uv=uv_proj, o=o_proj, g=g_proj)
         self.position = build_part("position", position) if position is not None else None
         self.q_cols = heads * (dim + rot_dim)
@@ -54,9 +64,11 @@ class LatentAttention:
     # -- what it needs ----------------------------------------------------------
     def tensors(self):
         n, H = self.names, self.heads
-        t = {n["q"]: TensorSpec((self.q_cols, self.hidden)), n["dkv"]: TensorSpec((self.rank + self.rot, self.hidden)),
-             n["cn"]: TensorSpec((self.rank,), init="gain"), n["uk"]: TensorSpec((H * self.dim, self.rank)),
+        t = {n["q"]: TensorSpec((self.q_cols, self.hidden)), n["uk"]: TensorSpec((H * self.dim, self.rank)),
              n["uv"]: TensorSpec((H * self.vdim, self.rank)), n["o"]: TensorSpec((self.hidden, H * self.vdim))}
+        if self.own_kv:
+            t[n["dkv"]] = TensorSpec((self.rank + self.rot, self.hidden))
+            t[n["cn"]] = TensorSpec((self.rank,), init="gain")
         if self.gate is not None:
             t[n["g"]] = TensorSpec((self.gate_cols, self.hidden))
         if self.position is not None:
@@ -64,15 +76,15 @@ class LatentAttention:
         return t
 
     def cache_need(self):
-        kind = "window" if self.window > 0 else "full"
-        return GroupSpec(kind, 1, self.rank + self.rot, planes=0, window=self.window, streams=1)
+        kind = "window" if self.cache_window > 0 else "full"
+        return GroupSpec(kind, 1, self.rank + self.rot, planes=0, window=self.cache_window, streams=1)
 
     def state_bytes(self) -> int:
         return 0
 
     def load(self, weights, device, dtype):
         n, H = self.names, self.heads
-        rows = [weights[n["q"]], weights[n["dkv"]]] + ([weights[n["g"]]] if self.gate is not None else [])
+        rows = [weights[n["q"]]] + ([weights[n["dkv"]]] if self.own_kv else []) + ([weights[n["g"]]] if self.gate is not None else [])
         total = sum(r.shape[0] for r in rows)
         if total % 8:
             # rows of zeros, so that a token's projection is a whole number of 16-byte pieces and kernels may read it by them
@@ -84,7 +96,7 @@ class LatentAttention:
         uk = weights[n["uk"]].reshape(H, self.dim, self.rank).transpose(1, 2)
         self.uk_t = compute_form(uk, device, dtype)
         self.uv = compute_form(weights[n["uv"]].reshape(H, self.vdim, self.rank), device, dtype)
-        self.c_gain = weights[n["cn"]].to(device).float().contiguous()
+        self.c_gain = weights[n["cn"]].to(device).float().contiguous() if self.own_kv else torch.ones(self.rank, dtype=torch.float32, device=device)
         if self.rank % 8 == 0 and ops.latent_attention_expanded_supported(dtype, self.dim, self.rot, self.vdim):
             # every head's key and value rows in one product over the latent vectors: [W_uk; W_uv]
             self.ukv = Linear(compute_form(torch.cat([weights[n["uk"]], weights[n["uv"]]], dim=0), device, dtype), role="kv_expand")
@@ -99,10 +111,13 @@ class LatentAttention:
             raise ValueError("latent attention rotates neighbouring pairs; its position encoding must offer that form")
         plane, _ = ctx.cache.plane(slot.group, slot.plane)
         table = ctx.cache.tables[slot.group]
-        proj = self.proj(x, ctx=ctx)                                   # [T, queries | latent row | gate]
+        if slot.writes != self.own_kv:
+            raise ValueError("a latent attention without a down-projection reads another run's cache plane, and only such a one does")
+        proj = self.proj(x, ctx=ctx)                                   # [T, queries | latent row (if its own) | gate]
+        kept = ("latent_rows", slot.group, slot.plane)                 # a step's compressed rows side by side, for the plane's readers
         if (self.ukv is not None and not ctx.decode and ctx.max_new_tokens >= EXPAND_FROM_TOKENS and ctx.host_starts
-                and not any(ctx.host_starts)):
-            out = self._attend_expanded(proj, rotary, plane if slot.writes else None, table, ctx)
+                and not any(ctx.host_starts) and (self.own_kv or kept in ctx.shared)):
+            out = self._attend_expanded(proj, rotary, plane if slot.writes else None, table, ctx, kept)
             self._gate_and_project(out, proj, residual, ctx, store)
             return
         q = torch.empty((T, H * dl), dtype=proj.dtype, device=proj.device)
@@ -124,21 +139,27 @@ class LatentAttention:
 
     def _gate_and_project(self, out, proj, residual, ctx, store: bool) -> None:
         if self.gate is not None:
-            g0 = self.q_cols + self.rank + self.rot
+            g0 = self.q_cols + (self.rank + self.rot if self.own_kv else 0)
             ops.sigmoid_gate(out, proj[:, g0:g0 + self.gate_cols], self.heads, self.vdim, self.gate == "head")
         if store:
             self.out_store(out, out=residual)
         else:
             self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
 
-    def _attend_expanded(self, proj, rotary, plane, table, ctx) -> torch.Tensor:
-        """Whole prompts from position 0: the cache rows are written as always and also kept side by side; one product
-        makes every head's keys and values from them; the attention runs per head on the tensor cores."""
+    def _attend_expanded(self, proj, rotary, plane, table, ctx, kept) -> torch.Tensor:
+        """Whole prompts from position 0: the cache rows are written as always and also kept side by side (for this layer and
+        for the layers that read its plane in the same step); one product makes every head's keys and values from them; the
+        attention runs per head on the tensor cores."""
         T, H = ctx.num_tokens, self.heads
-        rows = torch.empty((T, self.rank + self.rot), dtype=proj.dtype, device=proj.device)
+        if self.own_kv:
+            rows = torch.empty((T, self.rank + self.rot), dtype=proj.dtype, device=proj.device)
+            ctx.shared[kept] = rows
+        else:
+            rows = ctx.shared[kept]
         ops.latent_prep(proj, self.q_cols, None, plane, table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids,
                         self.c_gain, rotary.inv_freq if rotary else None, rotary.rope_dim if rotary else 0,
-                        rotary.amplitude if rotary else 1.0, self.eps, H, self.dim, self.rot, self.rank, rows_out=rows)
+                        rotary.amplitude if rotary else 1.0, self.eps, H, self.dim, self.rot, self.rank,
+                        rows_out=rows if self.own_kv else None)
         kv = self.ukv(rows[:, :self.rank], ctx=ctx)                    # [T, H * dim | H * vdim]
         out = torch.empty((T, H * self.vdim), dtype=proj.dtype, device=proj.device)
         ops.latent_attention_expanded(out, proj[:, :self.q_cols], kv[:, :H * self.dim], kv[:, H * self.dim:], rows[:, self.rank:],

@@ -81,3 +81,57 @@ class RMSNorm:
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class LayerNorm:
+    """Layer norm with a gain and no bias: y = (x - mean) / sqrt(variance + eps) * gain, the variance being the mean of the squared
+    deviations; all in float32.  It offers what RMSNorm offers to a block with norms before and after its sublayers (forward,
+    add_into, add_into_then, add_into_then_rows).  It cannot be folded into the products around it: a row has a mean to take
+    off besides its scale."""
+    graph_safe = True
+    foldable = False
+
+    def __init__(self, dim: int, eps: float, weight: str):
+        self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
+        self.gain = None
+
+    def tensors(self):
+        return {self.weight_name: TensorSpec((self.dim,), init="gain")}
+
+    def load(self, weights, device, dtype):
+        self.gain = compute_form(weights[self.weight_name], device, dtype)
+
+    def forward(self, x: torch.Tensor, ctx, out_dtype: torch.dtype, rows_index: torch.Tensor | None = None,
+                rows: int | None = None, scale: float = 1.0, fresh: bool = False):
+        if ctx is not None and getattr(ctx, "prenormed", None) is not None:
+            ctx.prenormed = None     # (left for another norm; this one always runs)
+        n = rows if rows is not None else (rows_index.shape[0] if rows_index is not None else x.shape[0])
+        out = torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
+        ops.layernorm(out, x, self.gain, self.eps, rows_index, scale)
+        return out
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual (float32) += norm(x)."""
+        ops.layernorm(residual, x, self.gain, self.eps, add=True)
+
+    def add_into_then(self, x: torch.Tensor, residual: torch.Tensor, following, out_dtype: torch.dtype) -> torch.Tensor:
+        """add_into, and what `following` (the norm that reads the residual next) makes of the new rows: one kernel where that
+        is a layer norm of the same width too, two otherwise."""
+        if isinstance(following, LayerNorm) and following.dim == self.dim and following.gain.dtype == self.gain.dtype \
+                and x.dtype == torch.float32 and x.shape == residual.shape:
+            out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+            ops.layernorm_add_norm(residual, x, self.gain, self.eps, out, following.gain, following.eps)
+            return out
+        self.add_into(x, residual)
+        return following.forward(residual, None, out_dtype, fresh=True)
+
+    def add_into_then_rows(self, x: torch.Tensor, residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        if out_dtype == residual.dtype:
+            self.add_into(x, residual)
+            return residual
+        out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        ops.layernorm_add_norm(residual, x, self.gain, self.eps, out, None, 0.0)
+        return out
+
+
+register_part("norm", "layernorm", LayerNorm)

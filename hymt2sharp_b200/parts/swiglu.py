@@ -59,3 +59,62 @@ class SwiGLU:
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class ClampedGLU:
+    """A gated feed-forward with biases and clamps:
+
+        g = min(W_gate x + b_gate, limit);  u = clamp(W_up x + b_up, -limit, limit);  y = g * sigmoid(alpha * g) * (u + 1);  out = W_down y + b_down
+
+    Gate and up are one product over the stacked weight; a small kernel adds the biases, clamps and applies the activation
+    (float32 arithmetic); the output bias is added behind the down product."""
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, hidden: int, intermediate: int, limit: float, alpha: float, gate_proj: str, up_proj: str, down_proj: str,
+                 gate_bias: str | None = None, up_bias: str | None = None, down_bias: str | None = None):
+        if (gate_bias is None) != (up_bias is None):
+            raise ValueError("the gate's and the up projection's biases come together or not at all")
+        if not limit > 0:
+            raise ValueError(f"a clamp at {limit}: the limit must be positive")
+        self.hidden, self.intermediate, self.limit, self.alpha = int(hidden), int(intermediate), float(limit), float(alpha)
+        self.names = dict(g=gate_proj, u=up_proj, d=down_proj, gb=gate_bias, ub=up_bias, db=down_bias)
+        self.gate_up = self.down = self.down_store = self.bias_in = self.bias_out = None
+
+    def tensors(self):
+        h, f, n = self.hidden, self.intermediate, self.names
+        t = {n["g"]: TensorSpec((f, h)), n["u"]: TensorSpec((f, h)), n["d"]: TensorSpec((h, f))}
+        if n["gb"] is not None:
+            t[n["gb"]] = TensorSpec((f,))
+            t[n["ub"]] = TensorSpec((f,))
+        if n["db"] is not None:
+            t[n["db"]] = TensorSpec((h,))
+        return t
+
+    def load(self, weights, device, dtype):
+        n = self.names
+        self.gate_up = Linear(compute_form(torch.cat([weights[n["g"]], weights[n["u"]]], dim=0), device, dtype), role="gate_up")
+        self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="down")
+        self.down_store = Linear(self.down.weight, ops.EPILOGUE_STORE, role="down")
+        if n["gb"] is not None:
+            self.bias_in = torch.cat([weights[n["gb"]], weights[n["ub"]]]).to(device).float().contiguous()
+        if n["db"] is not None:
+            self.bias_out = weights[n["db"]].to(device).float().contiguous()
+
+    def first_weights(self):
+        return self.gate_up.weight if self.gate_up is not None else None
+
+    def forward(self, x, residual: torch.Tensor, ctx, store: bool = False) -> None:
+        both = self.gate_up(x, ctx=ctx)
+        act = torch.empty((both.shape[0], self.intermediate), dtype=both.dtype, device=both.device)
+        ops.clamped_glu(act, both, self.bias_in, self.limit, self.alpha)
+        ctx.prenormed = None
+        if store:
+            self.down_store(act, out=residual)
+        else:
+            self.down(act, out=residual)
+        if self.bias_out is not None:
+            ops.bias_act(residual, self.bias_out, 0)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)
