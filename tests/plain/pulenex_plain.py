@@ -227,3 +227,13 @@ def forward(config: dict, W: dict, tokens, layers_out: list | None = None) -> to
         if layers_out is not None:
             layers_out.append(x.clone())
     return (layer_norm(x, W["final.norm"], eps) @ W["head"].T) * config.get("logit_scale", 1.0)
+
+
+def greedy(config: dict, W: dict, prompt, n: int) -> list:
+    """n tokens, each the argmax of the logits behind everything before it (the lowest index among equals)."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        t = int(torch.argmax(forward(config, W, toks)[-1]))
+        out.append(t)
+        toks.append(t)
+    return out
