@@ -140,7 +140,7 @@ def reference_arm() -> int:
     return 0
 
 
-# ---- another design beside the flagship: `--design pemezen`, `--design novunex`, `--design rutetar` ----------------------------
+# ---- another design beside the flagship: `--design pemezen`, `--design novunex`, `--design rutetar`, `--design pulenex` ----------------------------
 # Sizes that resemble a real model's layers (random weights), and a Hunyuan-dense model of the same width, depth and
 # nearly the same number of weights per layer beside it: the closest model that the library has.
 DESIGN_SIZES = {
@@ -214,7 +214,50 @@ def rutetar_config(size: str, layers: int):
                                         streams=z["streams"]))
 
 
-DESIGN_TABLES = {"pemezen": DESIGN_SIZES, "novunex": NOVUNEX_SIZES, "rutetar": RUTETAR_SIZES}
+# Pulenex: of every four layers the first is latent attention in a sliding window, the second retention with rotated q and k and
+# no feed-forward, the third runs chunked attention whose heads talk and the gated delta rule side by side, and the fourth is
+# latent attention that reads the first one's compressed rows; the feed-forward is dense, gated and clamped
+PULENEX_SIZES = {
+    "s": dict(width=1024, vocab=32768, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, window=1024, ret_heads=8, ret_dim=128, ret_vdim=128,
+              talk_heads=8, talk_kv_heads=2, talk_dim=128, chunk=1024, delta_heads=8, delta_kv_heads=4, delta_dim=128, delta_vdim=128,
+              ranks=64, taps=4, ff=2816, dense=DESIGN_SIZES["s"]["dense"]),
+    "m": dict(width=2048, vocab=65536, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=2048, ret_heads=16, ret_dim=128, ret_vdim=128,
+              talk_heads=16, talk_kv_heads=4, talk_dim=128, chunk=2048, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
+              ranks=64, taps=4, ff=5632, dense=DESIGN_SIZES["m"]["dense"]),
+}
+PULENEX_ORDER = ["latent", "retention", "parallel", "latent_from"]   # repeated up to --layers
+
+
+def pulenex_config(size: str, layers: int):
+    from hymt2sharp_b200.config.pulenex import PulenexConfig
+    z = PULENEX_SIZES[size]
+    entries, own = [], 0
+    for i in range(layers):
+        kind = PULENEX_ORDER[i % len(PULENEX_ORDER)]
+        mlp = dict(kind="dense", ff=z["ff"], limit=7.0)
+        if kind == "retention":
+            decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, z["ret_heads"] - 1)) for h in range(z["ret_heads"])]
+            entries.append(dict(type="retention", mlp=None, mixer=dict(heads=z["ret_heads"], dim=z["ret_dim"], vdim=z["ret_vdim"], decay=decay,
+                                                                       rot=dict(dims=z["ret_dim"] // 2, base=1000000.0))))
+        elif kind == "parallel":
+            left = dict(heads=z["talk_heads"], kv_heads=z["talk_kv_heads"], dim=z["talk_dim"], vdim=z["talk_dim"], scale=z["talk_dim"] ** -0.5,
+                        conv=z["taps"], mask=dict(size=z["chunk"]), rot=dict(dims=z["talk_dim"], base=10000.0))
+            right = dict(heads=z["delta_heads"], kv_heads=z["delta_kv_heads"], dim=z["delta_dim"], vdim=z["delta_vdim"], conv=z["taps"],
+                         decay_rank=z["ranks"], gate_rank=z["ranks"])
+            entries.append(dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp))
+        else:
+            mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+                         scale=(z["dim"] + z["rot_dim"]) ** -0.5, mask=dict(size=z["window"]), rot=dict(dims=z["rot_dim"], base=250000.0))
+            if kind == "latent_from":
+                mixer["kv_from"] = own
+            else:
+                own = i
+            entries.append(dict(type="latent_attention", mixer=mixer, mlp=mlp))
+    return PulenexConfig.from_dict(dict(architecture="Pulenex", vocab=z["vocab"], width=z["width"], layers=entries, norm=dict(eps=1e-6),
+                                        logit_scale=0.25))
+
+
+DESIGN_TABLES = {"pemezen": DESIGN_SIZES, "novunex": NOVUNEX_SIZES, "rutetar": RUTETAR_SIZES, "pulenex": PULENEX_SIZES}
 
 
 def make_design_models(size: str, layers: int, design: str = "pemezen") -> dict:
@@ -236,6 +279,8 @@ def make_design_models(size: str, layers: int, design: str = "pemezen") -> dict:
         new = novunex_config(size, layers)
     elif design == "rutetar":
         new = rutetar_config(size, layers)
+    elif design == "pulenex":
+        new = pulenex_config(size, layers)
     else:
         new = PemezenConfig.from_dict(dict(architecture="Pemezen", vocab=z["vocab"], width=z["width"], layers=entries,
                                            norm=dict(eps=1e-6, groups=2), canon=dict(taps=4), embedding=dict(scale=1.0), logit_softcap=30.0))
@@ -462,7 +507,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-kernels", action="store_true", help="skip the kernels timed alone")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--design", default=None, choices=["pemezen", "novunex", "rutetar"],
+    ap.add_argument("--design", default=None, choices=["pemezen", "novunex", "rutetar", "pulenex"],
                     help="instead of the flagship workload: prefill (--prefill tokens) and decode (--batch sequences of --prefill tokens, "
                          "--steps steps) of this design beside the Hunyuan-dense model of equal size, with per-kernel times")
     ap.add_argument("--design-size", default="s", choices=sorted(DESIGN_SIZES))

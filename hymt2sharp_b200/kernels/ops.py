@@ -853,7 +853,9 @@ def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: torch
         raise KernelError("causal_conv: the state rows are too short for this convolution")
     for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
         _need(t, n, torch.int32, 1)
-    stride = state.stride(0) if state.shape[1] else 0     # (a filter of one tap remembers nothing; the rows may then be empty)
+    stride = state.stride(0)
+    if taps == 1:      # a filter of one tap remembers nothing: the state rows are not touched, whatever their size and alignment
+        stride, state_offset = 0, 0
     _check(_lib().hymt2_causal_conv(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w), _ptr(bias), _ptr(state),
                                     c_long(state_offset), c_long(stride), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens),
                                     c_int(batch), c_int(max_new_tokens), c_int(C), c_int(taps), c_int(ldx), c_int(ldo),
