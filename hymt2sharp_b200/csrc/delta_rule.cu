@@ -7,10 +7,10 @@
 // q and k of every key head as unit vectors x / sqrt(sum(x^2) + unit_eps) (q also times q_scale), the decays
 // g = exp(-exp(A_log[h]) * softplus(x + dt_bias)) in place of x, and beta = sigmoid(.) in place.
 // `delta_scan` walks a sequence's new tokens.  The columns of S never meet (u's entry c needs column c only), so the grid
-// spreads them: a block holds COLS columns of one (sequence, head), TPC neighbouring lanes share a column and hold RPT of its
-// rows each in registers (dk <= RPT * TPC); the two sums over rows are finished with shuffles inside the TPC lanes.  The next
-// token's k, q and g are fetched while the current token is worked on.  S lies at byte `state_offset` of the sequence's state
-// row as [heads, dk, dv]; a sequence whose step starts at position 0 starts from zeros whatever the row holds; a padding row
+// spreads them: a block holds 16 columns of one (sequence, head), 8 neighbouring lanes share a column and hold RPT of its
+// rows each in registers (dk <= 8 * RPT); the two sums over rows are finished with shuffles inside those lanes.  The tokens'
+// vectors are staged through shared memory a group at a time, the next group being fetched while the current one is worked on.
+// S lies at byte `state_offset` of the sequence's state row as [heads, dk, dv]; a sequence whose step starts at position 0 starts from zeros whatever the row holds; a padding row
 // (slot < 0) writes zeros and remembers nothing.
 #include "common.cuh"
 
@@ -80,22 +80,31 @@ struct DeltaScanParams {
     int heads, kv_heads, dk, dv;
 };
 
-template <int TPC> __device__ __forceinline__ float part_sum(float v) {
+constexpr int DELTA_THREADS = 128, DELTA_TPC = 8, DELTA_COLS = DELTA_THREADS / DELTA_TPC, DELTA_GROUP = 8;
+
+__device__ __forceinline__ float part_sum(float v) {
 #pragma unroll
-    for (int o = TPC / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    for (int o = DELTA_TPC / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
-constexpr int DELTA_THREADS = 64;
-
-template <typename T, int RPT, int TPC>
+// A block holds DELTA_COLS columns of one (sequence, head)'s state; DELTA_TPC neighbouring lanes share a column and hold RPT of
+// its rows each in registers (dk <= DKP = RPT * DELTA_TPC; rows beyond dk are k = q = 0, g = 1 and stay zero).  The tokens' k, q,
+// g (float32), beta and the block's entries of v are staged through shared memory in groups of DELTA_GROUP tokens: while a group
+// is worked on, the next one is already on its way from global memory into registers.
+template <typename T, int RPT>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_scan_kernel(DeltaScanParams p) {
+    constexpr int DKP = RPT * DELTA_TPC;
+    constexpr int TOKEN = 3 * DKP + DELTA_COLS + 4;                    // staged floats a token: k, q, g, the block's v, beta (and three unused: 16-byte rows)
+    constexpr int ITEMS = DELTA_GROUP * TOKEN;
+    __shared__ __align__(16) float stage[ITEMS];
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int COLS = DELTA_THREADS / TPC;
     const int b = blockIdx.z, h = blockIdx.y;
-    const int c = blockIdx.x * COLS + threadIdx.x / TPC, part = threadIdx.x % TPC;
+    const int c0 = blockIdx.x * DELTA_COLS;
+    const int col = threadIdx.x / DELTA_TPC, part = threadIdx.x % DELTA_TPC;
+    const int c = c0 + col;
     const bool live = c < p.dv;
     const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
     if (n <= 0) return;
@@ -112,46 +121,94 @@ delta_scan_kernel(DeltaScanParams p) {
     float* S = (float*)(p.state + (size_t)slot * p.state_stride) + (size_t)h * p.dk * p.dv;
     float s[RPT];
 #pragma unroll
-    for (int i = 0; i < RPT; i++) s[i] = (start > 0 && live && r0 + i < p.dk) ? S[(size_t)(r0 + i) * p.dv + c] : 0.f;
+    for (int j = 0; j < RPT; j++) s[j] = (start > 0 && live && r0 + j < p.dk) ? S[(size_t)(r0 + j) * p.dv + c] : 0.f;
     const size_t kd = (size_t)p.kv_heads * p.dk, gd = (size_t)p.heads * p.dk;
-    const float* kp = p.k + (size_t)tok0 * kd + (size_t)kh * p.dk + r0;
-    const float* qp = p.q + (size_t)tok0 * kd + (size_t)kh * p.dk + r0;
-    const float* gp = p.decay + (size_t)tok0 * gd + (size_t)h * p.dk + r0;
-    float nk[RPT], nq[RPT], ng[RPT], nb, nv;
-    auto fetch = [&](int i) {
+    const float* kp = p.k + (size_t)tok0 * kd + (size_t)kh * p.dk;
+    const float* qp = p.q + (size_t)tok0 * kd + (size_t)kh * p.dk;
+    const float* gp = p.decay + (size_t)tok0 * gd + (size_t)h * p.dk;
+    const T* vp = (const T*)p.v + (size_t)tok0 * p.ldv + (size_t)h * p.dv + c0;
+    const float* bp = p.beta + (size_t)tok0 * p.ldb + h;
+    // Staging: thread t brings rows t, t + 128, ... of k, q and g of each of the group's tokens, one of the group's entries of v
+    // (token t / 16, column t % 16) and, the first eight threads, a token's beta.  A token behind the sequence's end is one that
+    // changes nothing (k = q = v = beta = 0, g = 1), so that a group is always walked whole; rows beyond dk the same.
+    // In shared memory the rows of k, q, g are interleaved so that the eight lanes of a column read their j-th four rows from
+    // eight neighbouring 16-byte pieces (row r = part * RPT + 4 j + x -> piece j * 8 + part, entry x).
+    static_assert(DELTA_GROUP * DELTA_COLS == DELTA_THREADS && DELTA_GROUP <= DELTA_THREADS, "one entry of v a thread");
+    constexpr int RP = (DKP + DELTA_THREADS - 1) / DELTA_THREADS;
+    int place[RP];
 #pragma unroll
-        for (int j = 0; j < RPT; j++) {
-            const bool in = r0 + j < p.dk;
-            nk[j] = in ? kp[(size_t)i * kd + j] : 0.f;
-            nq[j] = in ? qp[(size_t)i * kd + j] : 0.f;
-            ng[j] = in ? gp[(size_t)i * gd + j] : 1.f;
+    for (int x = 0; x < RP; x++) {
+        const int r = threadIdx.x + x * DELTA_THREADS;
+        place[x] = (((r % RPT) / 4) * DELTA_TPC + r / RPT) * 4 + (r % 4);
+    }
+    const int vt = threadIdx.x / DELTA_COLS, vc = threadIdx.x % DELTA_COLS;
+    float pre[DELTA_GROUP][3][RP], pre_v, pre_b;
+    auto fetch = [&](int i0) {
+#pragma unroll
+        for (int tt = 0; tt < DELTA_GROUP; tt++) {
+            const int i = i0 + tt;
+#pragma unroll
+            for (int x = 0; x < RP; x++) {
+                const int r = threadIdx.x + x * DELTA_THREADS;
+                const bool in = i < n && r < p.dk;
+                pre[tt][0][x] = in ? kp[(size_t)i * kd + r] : 0.f;
+                pre[tt][1][x] = in ? qp[(size_t)i * kd + r] : 0.f;
+                pre[tt][2][x] = in ? gp[(size_t)i * gd + r] : 1.f;
+            }
         }
-        nb = p.beta[(size_t)(tok0 + i) * p.ldb + h];
-        nv = live ? to_float(((const T*)p.v)[(size_t)(tok0 + i) * p.ldv + (size_t)h * p.dv + c]) : 0.f;
+        pre_v = (i0 + vt < n && c0 + vc < p.dv) ? to_float(vp[(size_t)(i0 + vt) * p.ldv + vc]) : 0.f;
+        pre_b = (threadIdx.x < DELTA_GROUP && i0 + (int)threadIdx.x < n) ? bp[(size_t)(i0 + threadIdx.x) * p.ldb] : 0.f;
     };
     fetch(0);
-    for (int i = 0; i < n; i++) {
-        float k[RPT], q[RPT], g[RPT];
+    for (int i0 = 0; i0 < n; i0 += DELTA_GROUP) {
+        __syncthreads();                       // the group before is no longer read
 #pragma unroll
-        for (int j = 0; j < RPT; j++) { k[j] = nk[j]; q[j] = nq[j]; g[j] = ng[j]; }
-        const float beta = nb, v = nv;
-        if (i + 1 < n) fetch(i + 1);
-        float pred = 0.f;
+        for (int tt = 0; tt < DELTA_GROUP; tt++)
 #pragma unroll
-        for (int j = 0; j < RPT; j++) {
-            s[j] *= g[j];
-            pred = fmaf(s[j], k[j], pred);
+            for (int x = 0; x < RP; x++)
+                if (threadIdx.x + x * DELTA_THREADS < DKP) {
+#pragma unroll
+                    for (int arr = 0; arr < 3; arr++) stage[tt * TOKEN + arr * DKP + place[x]] = pre[tt][arr][x];
+                }
+        stage[vt * TOKEN + 3 * DKP + vc] = pre_v;
+        if (threadIdx.x < DELTA_GROUP) stage[threadIdx.x * TOKEN + 3 * DKP + DELTA_COLS] = pre_b;
+        __syncthreads();
+        if (i0 + DELTA_GROUP < n) fetch(i0 + DELTA_GROUP);
+        float op[DELTA_GROUP];                 // every token's share of o, summed over the column's lanes behind the group
+#pragma unroll
+        for (int tt = 0; tt < DELTA_GROUP; tt++) {
+            const float* tk = stage + tt * TOKEN + part * 4;
+            const float* tq = tk + DKP;
+            const float* tg = tq + DKP;
+            const float v = stage[tt * TOKEN + 3 * DKP + col], beta = stage[tt * TOKEN + 3 * DKP + DELTA_COLS];
+            float k[RPT];
+            float pr[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < RPT; j += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(tk + j * DELTA_TPC), g4 = *reinterpret_cast<const float4*>(tg + j * DELTA_TPC);
+                k[j] = k4.x; k[j + 1] = k4.y; k[j + 2] = k4.z; k[j + 3] = k4.w;
+                s[j] *= g4.x; s[j + 1] *= g4.y; s[j + 2] *= g4.z; s[j + 3] *= g4.w;
+                pr[0] = fmaf(s[j], k4.x, pr[0]); pr[1] = fmaf(s[j + 1], k4.y, pr[1]);
+                pr[2] = fmaf(s[j + 2], k4.z, pr[2]); pr[3] = fmaf(s[j + 3], k4.w, pr[3]);
+            }
+            const float pred = part_sum((pr[0] + pr[1]) + (pr[2] + pr[3]));
+            const float u = beta * (v - pred);
+            float ou[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < RPT; j += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(tq + j * DELTA_TPC);
+                s[j] = fmaf(k[j], u, s[j]); s[j + 1] = fmaf(k[j + 1], u, s[j + 1]);
+                s[j + 2] = fmaf(k[j + 2], u, s[j + 2]); s[j + 3] = fmaf(k[j + 3], u, s[j + 3]);
+                ou[0] = fmaf(s[j], q4.x, ou[0]); ou[1] = fmaf(s[j + 1], q4.y, ou[1]);
+                ou[2] = fmaf(s[j + 2], q4.z, ou[2]); ou[3] = fmaf(s[j + 3], q4.w, ou[3]);
+            }
+            op[tt] = (ou[0] + ou[1]) + (ou[2] + ou[3]);
         }
-        pred = part_sum<TPC>(pred);
-        const float u = beta * (v - pred);
-        float o = 0.f;
 #pragma unroll
-        for (int j = 0; j < RPT; j++) {
-            s[j] = fmaf(k[j], u, s[j]);
-            o = fmaf(s[j], q[j], o);
+        for (int tt = 0; tt < DELTA_GROUP; tt++) {
+            const float o = part_sum(op[tt]);
+            if (live && part == 0 && i0 + tt < n) p.out[(size_t)(tok0 + i0 + tt) * hd + (size_t)h * p.dv + c] = o;
         }
-        o = part_sum<TPC>(o);
-        if (live && part == 0) p.out[(size_t)(tok0 + i) * hd + (size_t)h * p.dv + c] = o;
     }
     if (live) {
 #pragma unroll
@@ -189,16 +246,15 @@ HYMT2_API int hymt2_delta_scan(float* out, const float* q, const float* k, const
     p.out = out; p.q = q; p.k = k; p.decay = decay; p.beta = beta; p.v = v; p.state = (uint8_t*)state + state_offset;
     p.state_stride = state_stride; p.ldv = ldv; p.ldb = ldb; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
     p.heads = heads; p.kv_heads = kv_heads; p.dk = dk; p.dv = dv;
-#define DELTA_LAUNCH(RPT, TPC)                                                                                             \
-    do {                                                                                                                   \
-        const dim3 grid((dv + DELTA_THREADS / TPC - 1) / (DELTA_THREADS / TPC), heads, batch);                             \
-        HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_scan_kernel<T, RPT, TPC>, grid, dim3(DELTA_THREADS), 0, stream, p)); \
+#define DELTA_LAUNCH(RPT)                                                                                             \
+    do {                                                                                                              \
+        const dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, heads, batch);                                            \
+        HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_scan_kernel<T, RPT>, grid, dim3(DELTA_THREADS), 0, stream, p)); \
     } while (0)
-    if (dk <= 16) DELTA_LAUNCH(4, 4);
-    else if (dk <= 32) DELTA_LAUNCH(8, 4);
-    else if (dk <= 64) DELTA_LAUNCH(16, 4);
-    else if (dk <= 128) DELTA_LAUNCH(32, 4);
-    else DELTA_LAUNCH(32, 8);
+    if (dk <= 32) DELTA_LAUNCH(4);
+    else if (dk <= 64) DELTA_LAUNCH(8);
+    else if (dk <= 128) DELTA_LAUNCH(16);
+    else DELTA_LAUNCH(32);
 #undef DELTA_LAUNCH
     return hymt2_check_launch("delta_scan");
 }
