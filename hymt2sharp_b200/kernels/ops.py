@@ -1692,6 +1692,17 @@ def talk_prep(x: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None
                                   _ptr(inv_freq), c_int(rot_dims), c_int(T), c_int(heads), c_int(kv_heads), c_int(d), _stream()), "talk_prep")
 
 
+TALK_MMA_MIN_TOKENS = 8   # a sequence's new tokens from which a step's attention runs 16 queries a block on the tensor cores
+_talk_mma_ok: dict = {}
+
+
+def talking_attention_mma_supported(heads: int, kv_heads: int, d: int, block_tokens: int) -> bool:
+    key = (heads, kv_heads, d, block_tokens)
+    if key not in _talk_mma_ok:
+        _talk_mma_ok[key] = bool(_lib().hymt2_talking_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(d), c_int(block_tokens)))
+    return _talk_mma_ok[key]
+
+
 def talking_attention(out: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | None, k_plane: torch.Tensor, v_plane: torch.Tensor,
                       block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
                       max_new_tokens: int, heads: int, kv_heads: int, d: int, scale: float, talk: torch.Tensor, temp: torch.Tensor,
@@ -1715,6 +1726,15 @@ def talking_attention(out: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | N
     _need(block_table, "block_table", torch.int32, 2)
     for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
         _need(t, n, torch.int32, 1)
+    if out.dtype == torch.bfloat16 and max_new_tokens >= TALK_MMA_MIN_TOKENS and talking_attention_mma_supported(heads, kv_heads, d, k_plane.shape[2]) \
+            and (gate is None or (gate.data_ptr() % 2 == 0)):
+        # prompts in bfloat16: the two products on the tensor cores
+        _check(_lib().hymt2_talking_attention_mma(_ptr(out), _ptr(q), _ptr(gate), c_long(ldg), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
+                                                  c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens), _ptr(slot_ids),
+                                                  _ptr(kv_lens), c_int(batch), c_int(max_new_tokens), c_int(heads), c_int(kv_heads), c_int(d),
+                                                  c_float(scale), _ptr(talk), _ptr(temp), _ptr(sink), c_int(MASKS[mask]), c_int(mask_size),
+                                                  _stream()), "talking_attention_mma")
+        return
     _check(_lib().hymt2_talking_attention(_ptr(out), _ptr(q), _ptr(gate), c_long(ldg), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(out.dtype)),
                                           _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens),
                                           _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(max_new_tokens), c_int(heads), c_int(kv_heads),
