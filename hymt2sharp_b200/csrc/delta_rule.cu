@@ -80,7 +80,7 @@ struct DeltaScanParams {
     int heads, kv_heads, dk, dv;
 };
 
-constexpr int DELTA_THREADS = 128, DELTA_TPC = 8, DELTA_COLS = DELTA_THREADS / DELTA_TPC, DELTA_GROUP = 8;
+constexpr int DELTA_THREADS = 128, DELTA_TPC = 8, DELTA_COLS = DELTA_THREADS / DELTA_TPC;
 
 __device__ __forceinline__ float part_sum(float v) {
 #pragma unroll
@@ -91,8 +91,9 @@ __device__ __forceinline__ float part_sum(float v) {
 // A block holds DELTA_COLS columns of one (sequence, head)'s state; DELTA_TPC neighbouring lanes share a column and hold RPT of
 // its rows each in registers (dk <= DKP = RPT * DELTA_TPC; rows beyond dk are k = q = 0, g = 1 and stay zero).  The tokens' k, q,
 // g (float32), beta and the block's entries of v are staged through shared memory in groups of DELTA_GROUP tokens: while a group
-// is worked on, the next one is already on its way from global memory into registers.
-template <typename T, int RPT>
+// is worked on, the next one is already on its way from global memory into registers.  Steps of one token a sequence take the
+// instance with groups of one: a fraction of the registers, so that many more blocks stream their states at once.
+template <typename T, int RPT, int DELTA_GROUP>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_scan_kernel(DeltaScanParams p) {
     constexpr int DKP = RPT * DELTA_TPC;
@@ -133,7 +134,7 @@ delta_scan_kernel(DeltaScanParams p) {
     // changes nothing (k = q = v = beta = 0, g = 1), so that a group is always walked whole; rows beyond dk the same.
     // In shared memory the rows of k, q, g are interleaved so that the eight lanes of a column read their j-th four rows from
     // eight neighbouring 16-byte pieces (row r = part * RPT + 4 j + x -> piece j * 8 + part, entry x).
-    static_assert(DELTA_GROUP * DELTA_COLS == DELTA_THREADS && DELTA_GROUP <= DELTA_THREADS, "one entry of v a thread");
+    static_assert(DELTA_GROUP * DELTA_COLS <= DELTA_THREADS, "at most one entry of v a thread");
     constexpr int RP = (DKP + DELTA_THREADS - 1) / DELTA_THREADS;
     int place[RP];
 #pragma unroll
@@ -156,7 +157,7 @@ delta_scan_kernel(DeltaScanParams p) {
                 pre[tt][2][x] = in ? gp[(size_t)i * gd + r] : 1.f;
             }
         }
-        pre_v = (i0 + vt < n && c0 + vc < p.dv) ? to_float(vp[(size_t)(i0 + vt) * p.ldv + vc]) : 0.f;
+        pre_v = (vt < DELTA_GROUP && i0 + vt < n && c0 + vc < p.dv) ? to_float(vp[(size_t)(i0 + vt) * p.ldv + vc]) : 0.f;
         pre_b = (threadIdx.x < DELTA_GROUP && i0 + (int)threadIdx.x < n) ? bp[(size_t)(i0 + threadIdx.x) * p.ldb] : 0.f;
     };
     fetch(0);
@@ -170,7 +171,7 @@ delta_scan_kernel(DeltaScanParams p) {
 #pragma unroll
                     for (int arr = 0; arr < 3; arr++) stage[tt * TOKEN + arr * DKP + place[x]] = pre[tt][arr][x];
                 }
-        stage[vt * TOKEN + 3 * DKP + vc] = pre_v;
+        if (vt < DELTA_GROUP) stage[vt * TOKEN + 3 * DKP + vc] = pre_v;
         if (threadIdx.x < DELTA_GROUP) stage[threadIdx.x * TOKEN + 3 * DKP + DELTA_COLS] = pre_b;
         __syncthreads();
         if (i0 + DELTA_GROUP < n) fetch(i0 + DELTA_GROUP);
@@ -235,8 +236,8 @@ HYMT2_API int hymt2_delta_scan_max_dk() { return 256; }
 
 HYMT2_API int hymt2_delta_scan(float* out, const float* q, const float* k, const float* decay, const float* beta, long ldb, const void* v,
                                long ldv, int dtype, void* state, long state_offset, long state_stride, const int* cu_seqlens,
-                               const int* slot_ids, const int* kv_lens, int batch, int heads, int kv_heads, int dk, int dv,
-                               cudaStream_t stream) {
+                               const int* slot_ids, const int* kv_lens, int batch, int max_new_tokens, int heads, int kv_heads, int dk,
+                               int dv, cudaStream_t stream) {
     if (batch == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && batch <= 65535 && heads > 0 && heads <= 65535 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0,
                   "delta_scan: bad sizes");
@@ -249,7 +250,10 @@ HYMT2_API int hymt2_delta_scan(float* out, const float* q, const float* k, const
 #define DELTA_LAUNCH(RPT)                                                                                             \
     do {                                                                                                              \
         const dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, heads, batch);                                            \
-        HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_scan_kernel<T, RPT>, grid, dim3(DELTA_THREADS), 0, stream, p)); \
+        if (max_new_tokens == 1)                                                                                      \
+            HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_scan_kernel<T, RPT, 1>, grid, dim3(DELTA_THREADS), 0, stream, p)); \
+        else                                                                                                          \
+            HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_scan_kernel<T, RPT, 8>, grid, dim3(DELTA_THREADS), 0, stream, p)); \
     } while (0)
     if (dk <= 32) DELTA_LAUNCH(4);
     else if (dk <= 64) DELTA_LAUNCH(8);

@@ -4,7 +4,8 @@
 // block with norms before AND after its sublayers needs: stored (optionally of gathered rows, optionally scaled), added
 // into float32 rows, and "added, then the next norm of the new rows" in one launch.  And the sum of several branches, each
 // divided by its own root mean square and multiplied by its own gain: out = sum_b scale_b * x_b / sqrt(mean(x_b^2) + eps) * gain_b.
-// One block per row; a row is read from global memory in every pass (it stays in L1/L2 between them).
+// One block per row.  Rows of up to 8,192 entries stay in registers between the passes (eight entries a thread); wider rows are
+// read from global memory in every pass (they stay in L1/L2 between them).
 #include "common.cuh"
 
 namespace {
@@ -76,6 +77,112 @@ __global__ void layernorm_add_norm_kernel(float* __restrict__ y, const float* __
     for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = from_float<TH>((res[i] - mean_b) * scale_b * to_float(gain_b[i]));
 }
 
+// The same two kernels for rows of at most PER entries a thread: a thread's entries stay in registers between the passes, so a
+// row is read once and the passes do not wait for memory again.
+constexpr int LN_PER = 8;
+
+template <typename TX, typename TW, typename TY, bool ADD>
+__global__ void layernorm_cached_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
+                                        const int* __restrict__ rows_index, int dim, float eps, float out_scale) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim;
+    float v[LN_PER], s = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = i < dim ? to_float(src[i]) : 0.f;
+        s += v[j];
+    }
+    const float mean = block_sum(s, scratch) / (float)dim;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float d = i < dim ? v[j] - mean : 0.f;
+        q = fmaf(d, d, q);
+    }
+    const float scale = 1.0f / sqrtf(block_sum(q, scratch) / (float)dim + eps);
+    TY* dst = y + (size_t)r * dim;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < dim) {
+            float o = (v[j] - mean) * scale * to_float(gain[i]);
+            if (out_scale != 1.0f) o *= out_scale;
+            if constexpr (ADD) dst[i] = from_float<TY>(to_float(dst[i]) + o);
+            else dst[i] = from_float<TY>(o);
+        }
+    }
+}
+
+template <typename TW, typename TH>
+__global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const float* __restrict__ x, const TW* __restrict__ gain_a,
+                                                 TH* __restrict__ h, const TW* __restrict__ gain_b, int dim, float eps_a, float eps_b) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t off = (size_t)blockIdx.x * dim;
+    float v[LN_PER], old[LN_PER], s = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = i < dim ? x[off + i] : 0.f;
+        old[j] = i < dim ? y[off + i] : 0.f;
+        s += v[j];
+    }
+    const float mean = block_sum(s, scratch) / (float)dim;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float d = i < dim ? v[j] - mean : 0.f;
+        q = fmaf(d, d, q);
+    }
+    const float scale_a = 1.0f / sqrtf(block_sum(q, scratch) / (float)dim + eps_a);
+    float s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < dim) {
+            v[j] = old[j] + (v[j] - mean) * scale_a * to_float(gain_a[i]);
+            y[off + i] = v[j];
+            s2 += v[j];
+        }
+    }
+    if (gain_b == nullptr) {
+#pragma unroll
+        for (int j = 0; j < LN_PER; j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < dim) h[off + i] = from_float<TH>(v[j]);
+        }
+        return;
+    }
+    const float mean_b = block_sum(s2, scratch) / (float)dim;
+    float q2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float d = i < dim ? v[j] - mean_b : 0.f;
+        q2 = fmaf(d, d, q2);
+    }
+    const float scale_b = 1.0f / sqrtf(block_sum(q2, scratch) / (float)dim + eps_b);
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < dim) h[off + i] = from_float<TH>((v[j] - mean_b) * scale_b * to_float(gain_b[i]));
+    }
+}
+
+// threads of a block whose rows fit LN_PER entries a thread (0: they do not)
+inline int cached_threads(int dim) {
+    for (int t = 64; t <= 1024; t *= 2)
+        if (t * LN_PER >= dim) return t;
+    return 0;
+}
+
 constexpr int MAX_NORMED_BRANCHES = 4;
 struct BranchSumParams {
     const float* x[MAX_NORMED_BRANCHES];
@@ -121,6 +228,18 @@ HYMT2_API int hymt2_layernorm(void* y, int y_dtype, const void* x, int x_dtype, 
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
     HYMT2_REQUIRE(!add || y_dtype == HYMT2_F32, "layernorm: adding into the output needs float32 rows");
+    if (const int ct = cached_threads(dim)) {
+        HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
+            if (add) {
+                launch_pdl(layernorm_cached_kernel<TX, TW, float, true>, dim3(rows), dim3(ct), 0, stream, (float*)y, (const TX*)x, (const TW*)gain,
+                           rows_index, dim, eps, out_scale);
+            } else {
+                HYMT2_DISPATCH_DTYPE(y_dtype, TY, (launch_pdl(layernorm_cached_kernel<TX, TW, TY, false>, dim3(rows), dim3(ct), 0, stream, (TY*)y,
+                                                              (const TX*)x, (const TW*)gain, rows_index, dim, eps, out_scale)));
+            }
+        }));
+        return hymt2_check_launch("layernorm");
+    }
     const int threads = norm_threads(dim);
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
         if (add) {
@@ -138,6 +257,12 @@ HYMT2_API int hymt2_layernorm_add_norm(float* y, const float* x, const void* gai
                                        int rows, int dim, float eps_a, float eps_b, cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
+    if (const int ct = cached_threads(dim)) {
+        HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
+            (launch_pdl(layernorm_add_norm_cached_kernel<TW, TH>, dim3(rows), dim3(ct), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
+                        (const TW*)gain_b, dim, eps_a, eps_b))));
+        return hymt2_check_launch("layernorm_add_norm");
+    }
     HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
         (launch_pdl(layernorm_add_norm_kernel<TW, TH>, dim3(rows), dim3(norm_threads(dim)), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
                     (const TW*)gain_b, dim, eps_a, eps_b))));

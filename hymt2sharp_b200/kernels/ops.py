@@ -1767,10 +1767,11 @@ def delta_prep(qk: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, decay: torc
 
 def delta_scan(out: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, v: torch.Tensor,
                state: torch.Tensor, state_offset: int, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
-               heads: int, kv_heads: int, dk: int, dv: int) -> None:
+               heads: int, kv_heads: int, dk: int, dv: int, max_new_tokens: int = 0) -> None:
     """Per (sequence, head), S [dk, dv] float32 at byte `state_offset` of the state row as [heads, dk, dv] (ignored by a sequence that
     starts at position 0): S = diag(decay_t) S; u = beta_t (v_t - S^T k_t); S += k_t u^T; out_t = S^T q_t.  qn, kn, decay, beta as
-    delta_prep leaves them; v [T, heads * dv] in the compute type (rows may be columns of a wider matrix); out float32."""
+    delta_prep leaves them; v [T, heads * dv] in the compute type (rows may be columns of a wider matrix); out float32.
+    `max_new_tokens`: the longest sequence's new tokens (1 picks the instance made for decode steps; 0: unknown)."""
     _need(out, "out", torch.float32, 2); _need(qn, "qn", torch.float32, 2); _need(kn, "kn", torch.float32, 2); _need(decay, "decay", torch.float32, 2)
     T = out.shape[0]
     ldv, ldb = _rows_view(v, "v"), _rows_view(beta, "beta", torch.float32)
@@ -1783,5 +1784,5 @@ def delta_scan(out: torch.Tensor, qn: torch.Tensor, kn: torch.Tensor, decay: tor
         _need(t, n, torch.int32, 1)
     _check(_lib().hymt2_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(decay), _ptr(beta), c_long(ldb), _ptr(v), c_long(ldv),
                                    c_int(dtype_code(v.dtype)), _ptr(state), c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens),
-                                   _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
-                                   _stream()), "delta_scan")
+                                   _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(max_new_tokens), c_int(heads), c_int(kv_heads), c_int(dk),
+                                   c_int(dv), _stream()), "delta_scan")

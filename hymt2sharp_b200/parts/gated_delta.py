@@ -103,7 +103,7 @@ class GatedDelta:
         ops.delta_prep(qkv[:, :2 * kd], qn, kn, decay, beta, self.dt_bias, self.a_log, H, G, d, d ** -0.5, UNIT_EPS)
         o = torch.empty((T, H * dv), dtype=torch.float32, device=proj.device)
         ops.delta_scan(o, qn, kn, decay, beta, qkv[:, 2 * kd:], ctx.cache.state, slot.state_offset, ctx.cu_seqlens, ctx.slot_ids,
-                       ctx.kv_lens, ctx.num_seqs, H, G, d, dv)
+                       ctx.kv_lens, ctx.num_seqs, H, G, d, dv, ctx.max_new_tokens)
         gated = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
         ops.head_norm_gate(gated, o, gate, self.gain, H, dv, self.eps, gate_act="sigmoid")
         if store:
