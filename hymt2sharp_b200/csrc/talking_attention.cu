@@ -172,7 +172,7 @@ talking_attention_kernel(TalkParams p) {
     const int lo = lowest_seen(pos_first, p.mask_kind, p.mask_size);
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     for (int k0 = lo / bk * bk; k0 <= pos_last; k0 += bk) {
-        __syncthreads();   // the tiles and scores of the round before are no longer read; first round: Q, O, mix are written
+        __syncthreads();   // the tiles and scores of the tile before are no longer read; first tile: Q, O, mix are written
         // -- the key and value tiles: row kj holds position k0 + kj for all key heads; rows that no query of the block sees are zeros
         {
             const int block = table[k0 / p.block_tokens];

@@ -143,8 +143,8 @@ talking_attention_mma_kernel(TalkMmaParams p) {
     const int f0 = warp * per_warp;
 
     // A tile of keys or of values on its way into shared memory: eight threads a row, 16 bytes a piece; a row that no query of
-    // the block sees is zeros.  The key tile of round n + 1 is asked for as soon as round n's scores are made, the value tile
-    // of round n at its start: both arrive under the round's other work.
+    // the block sees is zeros.  The key tile of pass n + 1 is asked for as soon as pass n's scores are made, the value tile
+    // of pass n at its start: both arrive under the other work of the pass.
     auto ask_tile = [&](bf16* dst, const bf16* cache, int k0) {
         if (k0 <= pos_last) {
             const int block = table[k0 / p.block_tokens], off = k0 % p.block_tokens;
@@ -161,9 +161,9 @@ talking_attention_mma_kernel(TalkMmaParams p) {
     const int k_first = lo / TM_BK * TM_BK;
     ask_tile(Ks, p.k_cache, k_first);
     for (int k0 = k_first; k0 <= pos_last; k0 += TM_BK) {
-        __syncthreads();   // the value tile and the weights of the round before are no longer read (first round: Q, mix, the rows' openings)
+        __syncthreads();   // the value tile and the weights of the pass before are no longer read (first pass: Q, mix, the rows' openings)
         ask_tile(Vs, p.v_cache, k0);
-        tm_wait_but_one();  // this round's keys are here (the values may still be on their way)
+        tm_wait_but_one();  // the keys of this pass are here (the values may still be on their way)
         __syncthreads();
         // -- raw scores: a warp takes a head, both halves of the key tile share the head's query fragments
         for (int h = warp; h < H; h += TM_WARPS) {
@@ -185,7 +185,7 @@ talking_attention_mma_kernel(TalkMmaParams p) {
             wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD + 16, s1, TM_SLD, wmma::mem_row_major);
         }
         __syncthreads();
-        ask_tile(Ks, p.k_cache, k0 + TM_BK);   // the key tile is free: the next round's keys (or an empty group behind the last round)
+        ask_tile(Ks, p.k_cache, k0 + TM_BK);   // the key tile is free: the keys of the next pass (or an empty group behind the last pass)
         // -- the heads talk; then the mask.  A thread owns a (query, key) pair across all heads, so the mixing is in place.
         for (int pair = tid; pair < TM_BQ * TM_BK; pair += TM_THREADS) {
             const int qi = pair / TM_BK, kj = pair % TM_BK;
@@ -236,7 +236,7 @@ talking_attention_mma_kernel(TalkMmaParams p) {
             run_l[row] = run_l[row] * a + sum;
             run_m[row] = m_new;
         }
-        tm_wait_but_one();   // this round's values are here (the next round's keys may still be on their way)
+        tm_wait_but_one();   // the values of this pass are here (the keys of the next pass may still be on their way)
         __syncthreads();
         // -- O = shrink O + P V
         {
