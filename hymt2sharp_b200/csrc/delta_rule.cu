@@ -39,7 +39,9 @@ delta_prep_kernel(DeltaPrepParams p) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* row = (const T*)p.qk + (size_t)t * p.ldqk;
     const int kd = p.kv_heads * p.dk;
-    for (int item = warp; item < 2 * p.kv_heads; item += 4) {     // (q or k, key head)
+    // (the blocks of a token share its work among themselves: blockIdx.y of gridDim.y)
+    const int share = blockIdx.y, shares = gridDim.y;
+    for (int item = warp + 4 * share; item < 2 * p.kv_heads; item += 4 * shares) {     // (q or k, key head)
         const bool is_k = item >= p.kv_heads;
         const int g = is_k ? item - p.kv_heads : item;
         const T* src = row + (is_k ? kd : 0) + (size_t)g * p.dk;
@@ -55,11 +57,11 @@ delta_prep_kernel(DeltaPrepParams p) {
     }
     const int hd = p.heads * p.dk;
     float* dec = p.decay + (size_t)t * hd;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    for (int i = threadIdx.x + share * blockDim.x; i < hd; i += blockDim.x * shares) {
         const float rate = expf(p.a_log[i / p.dk]);
         dec[i] = expf(-rate * softplus_f(dec[i] + p.dt_bias[i]));
     }
-    for (int i = threadIdx.x; i < p.heads; i += blockDim.x) {
+    for (int i = threadIdx.x + share * blockDim.x; i < p.heads; i += blockDim.x * shares) {
         float* b = p.beta + (size_t)t * p.ldb + i;
         *b = 1.0f / (1.0f + expf(-*b));
     }
@@ -228,7 +230,8 @@ HYMT2_API int hymt2_delta_prep(const void* qk, long ldqk, int dtype, float* qn, 
     DeltaPrepParams p;
     p.qk = qk; p.qn = qn; p.kn = kn; p.decay = decay; p.beta = beta; p.dt_bias = dt_bias; p.a_log = a_log; p.ldqk = ldqk; p.ldb = ldb;
     p.heads = heads; p.kv_heads = kv_heads; p.dk = dk; p.q_scale = q_scale; p.unit_eps = unit_eps;
-    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_prep_kernel<T>, dim3(tokens), dim3(128), 0, stream, p));
+    const int shares = tokens >= 512 ? 1 : (heads * dk >= 2048 ? 8 : (heads * dk >= 512 ? 2 : 1));   // few tokens: several blocks a token
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(delta_prep_kernel<T>, dim3(tokens, shares), dim3(128), 0, stream, p));
     return hymt2_check_launch("delta_prep");
 }
 

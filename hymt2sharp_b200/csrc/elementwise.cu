@@ -281,8 +281,10 @@ rotate_heads_kernel(TY* __restrict__ y, long ldy, const TX* __restrict__ x, long
     const TX* src = x + (size_t)t * ldx;
     TY* dst = y + (size_t)t * ldy;
     const int per = half + (d - rot_dims);
-    for (int item = threadIdx.x; item < heads * per; item += blockDim.x) {
-        const int h = item / per, i = item - h * per;
+    // (the blocks of a token share its heads and its copied columns among themselves)
+    const int h_lo = (int)((long)heads * blockIdx.y / gridDim.y), h_hi = (int)((long)heads * (blockIdx.y + 1) / gridDim.y);
+    for (int item = threadIdx.x; item < (h_hi - h_lo) * per; item += blockDim.x) {
+        const int h = h_lo + item / per, i = item % per;
         const TX* s = src + (size_t)h * d;
         TY* o = dst + (size_t)h * d;
         if (i < half) {
@@ -296,7 +298,7 @@ rotate_heads_kernel(TY* __restrict__ y, long ldy, const TX* __restrict__ x, long
         }
     }
     if ((const void*)src != (const void*)dst || sizeof(TX) != sizeof(TY))
-        for (int c = heads * d + threadIdx.x; c < cols; c += blockDim.x) dst[c] = from_float<TY>(to_float(src[c]));
+        for (int c = heads * d + blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += blockDim.x * gridDim.y) dst[c] = from_float<TY>(to_float(src[c]));
 }
 
 HYMT2_API int hymt2_rotate_heads(void* y, int y_dtype, long ldy, const void* x, int x_dtype, long ldx, const int* token_pos,
@@ -308,7 +310,7 @@ HYMT2_API int hymt2_rotate_heads(void* y, int y_dtype, long ldy, const void* x, 
                   "rotate_heads: %d rotated entries of %d", rot_dims, d);
     const size_t smem = sizeof(float) * (size_t)(rot_dims + 2);
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(y_dtype, TY,
-        (launch_pdl(rotate_heads_kernel<TX, TY>, dim3(tokens), dim3(128), smem, stream, (TY*)y, ldy, (const TX*)x, ldx, token_pos, inv_freq,
+        (launch_pdl(rotate_heads_kernel<TX, TY>, dim3(tokens, tokens >= 512 ? 1 : (cols >= 2048 ? 8 : (cols >= 512 ? 2 : 1))), dim3(128), smem, stream, (TY*)y, ldy, (const TX*)x, ldx, token_pos, inv_freq,
                     heads, d, rot_dims, pairing, cols))));
     return hymt2_check_launch("rotate_heads");
 }

@@ -108,6 +108,11 @@ struct TalkParams {
     long ldg;
     int table_stride, block_tokens, heads, kv_heads, d, mask_kind, mask_size, bk;
     float scale;
+    // decode steps whose queries may see many keys: split s of a sequence takes the key tiles [s * split_keys, (s + 1) * split_keys)
+    // behind the first tile that the query sees, and leaves its unnormalised sums (no sink, no gate) for `talk_merge`
+    int split_keys, max_splits;
+    float* part_o;         // [sequences, max_splits, heads * d]
+    float* part_ml;        // [sequences, max_splits, 2 * heads]: running maximum, running sum
 };
 
 constexpr int TALK_THREADS = 256;
@@ -129,15 +134,21 @@ talking_attention_kernel(TalkParams p) {
     pdl_launch_dependents();
     const int b = blockIdx.y;
     const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
-    const int q0 = blockIdx.x * BQ;
+    const bool split = p.split_keys > 0;                // (then BQ is 1 and blockIdx.x names the split)
+    const int q0 = split ? 0 : blockIdx.x * BQ;
     if (q0 >= n) return;
     const int nq = min(BQ, n - q0);
     const int slot = p.slot_ids[b];
     const int H = p.heads, G = p.kv_heads, d = p.d, bk = p.bk, rep = H / G;
     const int hd = H * d;
     T* out = (T*)p.out + (size_t)(tok0 + q0) * hd;
+    float* my_o = split ? p.part_o + ((size_t)b * p.max_splits + blockIdx.x) * hd : nullptr;
+    float* my_ml = split ? p.part_ml + ((size_t)b * p.max_splits + blockIdx.x) * 2 * H : nullptr;
     if (slot < 0) {   // a padding row: a defined output, nothing read
-        for (int i = threadIdx.x; i < nq * hd; i += TALK_THREADS) out[i] = from_float<T>(0.f);
+        if (!split)
+            for (int i = threadIdx.x; i < nq * hd; i += TALK_THREADS) out[i] = from_float<T>(0.f);
+        else
+            for (int i = threadIdx.x; i < H; i += TALK_THREADS) { my_ml[i] = -INFINITY; my_ml[H + i] = 0.f; }
         return;
     }
     const int start = p.kv_lens[b] - n;                 // position of the sequence's first new token
@@ -160,9 +171,9 @@ talking_attention_kernel(TalkParams p) {
 
     for (int i = threadIdx.x; i < H * H; i += TALK_THREADS) mix[i] = p.talk[i] * p.temp[i % H] * p.scale;
     for (int i = threadIdx.x; i < BQ * H; i += TALK_THREADS) {
-        const float s = p.sink ? p.sink[i % H] : -INFINITY;
-        run_m[i] = s;                                    // the sink opens every row: maximum sink_h, sum exp(sink_h - sink_h) = 1
-        run_l[i] = p.sink ? 1.f : 0.f;
+        const bool opens = p.sink && !split;            // (a split's rows open empty: the merge brings the sink in)
+        run_m[i] = opens ? p.sink[i % H] : -INFINITY;   // the sink opens every row: maximum sink_h, sum exp(sink_h - sink_h) = 1
+        run_l[i] = opens ? 1.f : 0.f;
     }
     const T* qsrc = (const T*)p.q + (size_t)(tok0 + q0) * hd;
     for (int i = threadIdx.x; i < BQ * hd; i += TALK_THREADS) {
@@ -171,28 +182,36 @@ talking_attention_kernel(TalkParams p) {
     }
     const int lo = lowest_seen(pos_first, p.mask_kind, p.mask_size);
     const int* table = p.block_table + (size_t)slot * p.table_stride;
-    for (int k0 = lo / bk * bk; k0 <= pos_last; k0 += bk) {
+    int k_begin = lo / bk * bk, k_end = pos_last;
+    if (split) {
+        k_begin += blockIdx.x * p.split_keys;
+        k_end = min(k_end, k_begin + p.split_keys - 1);
+    }
+    for (int k0 = k_begin; k0 <= k_end; k0 += bk) {
         __syncthreads();   // the tiles and scores of the tile before are no longer read; first tile: Q, O, mix are written
         // -- the key and value tiles: row kj holds position k0 + kj for all key heads; rows that no query of the block sees are zeros
         {
             const int block = table[k0 / p.block_tokens];
             const int off = k0 % p.block_tokens;
-            const int per_row = G * d / VEC;
-            for (int i = threadIdx.x; i < bk * per_row; i += TALK_THREADS) {
-                const int kj = i / per_row, e = (i - kj * per_row) * VEC;
-                const int g = e / d, x = e - g * d;
+            // eight threads a key row (a row's pieces are shared out among them, head by head)
+            for (int kj = threadIdx.x >> 3; kj < bk; kj += TALK_THREADS >> 3) {
                 const int pos = k0 + kj;
-                Pack<T, VEC> kv, vv;
-                if (pos >= lo && pos <= pos_last && block >= 0) {
-                    const size_t src = (((size_t)block * G + g) * p.block_tokens + off + kj) * d + x;
-                    kv = load_pack<T, VEC>((const T*)p.k_cache + src);
-                    vv = load_pack<T, VEC>((const T*)p.v_cache + src);
-                } else {
+                const bool live_row = pos >= lo && pos <= pos_last && block >= 0;
+                for (int g = 0; g < G; g++) {
+                    const size_t src = (((size_t)(live_row ? block : 0) * G + g) * p.block_tokens + off + kj) * d;
+                    for (int x = (threadIdx.x & 7) * VEC; x < d; x += 8 * VEC) {
+                        Pack<T, VEC> kv, vv;
+                        if (live_row) {
+                            kv = load_pack<T, VEC>((const T*)p.k_cache + src + x);
+                            vv = load_pack<T, VEC>((const T*)p.v_cache + src + x);
+                        } else {
 #pragma unroll
-                    for (int z = 0; z < VEC; z++) kv.v[z] = vv.v[z] = from_float<T>(0.f);
+                            for (int z = 0; z < VEC; z++) kv.v[z] = vv.v[z] = from_float<T>(0.f);
+                        }
+                        store_pack<T, VEC>(Kt + (size_t)kj * row_k + (size_t)g * d + x, kv);
+                        store_pack<T, VEC>(Vt + (size_t)kj * row_k + (size_t)g * d + x, vv);
+                    }
                 }
-                store_pack<T, VEC>(Kt + (size_t)kj * row_k + e, kv);
-                store_pack<T, VEC>(Vt + (size_t)kj * row_k + e, vv);
             }
         }
         __syncthreads();
@@ -204,16 +223,30 @@ talking_attention_kernel(TalkParams p) {
             float acc[BQ];
 #pragma unroll
             for (int qi = 0; qi < BQ; qi++) acc[qi] = 0.f;
-            for (int e = 0; e < d; e += VEC) {
-                const Pack<T, VEC> kv = load_pack<T, VEC>(kr + e);
-                float kf[VEC];
+            if constexpr (BQ == 1 && VEC > 1) {       // one query: VEC sums side by side instead of one long chain
+                float part[VEC];
 #pragma unroll
-                for (int z = 0; z < VEC; z++) kf[z] = to_float(kv.v[z]);
+                for (int z = 0; z < VEC; z++) part[z] = 0.f;
+#pragma unroll 4
+                for (int e = 0; e < d; e += VEC) {
+                    const Pack<T, VEC> kv = load_pack<T, VEC>(kr + e);
 #pragma unroll
-                for (int qi = 0; qi < BQ; qi++) {
-                    const float* qq = qh + (size_t)qi * hd + e;
+                    for (int z = 0; z < VEC; z++) part[z] = fmaf(qh[e + z], to_float(kv.v[z]), part[z]);
+                }
 #pragma unroll
-                    for (int z = 0; z < VEC; z++) acc[qi] = fmaf(qq[z], kf[z], acc[qi]);
+                for (int z = 0; z < VEC; z++) acc[0] += part[z];
+            } else {
+                for (int e = 0; e < d; e += VEC) {
+                    const Pack<T, VEC> kv = load_pack<T, VEC>(kr + e);
+                    float kf[VEC];
+#pragma unroll
+                    for (int z = 0; z < VEC; z++) kf[z] = to_float(kv.v[z]);
+#pragma unroll
+                    for (int qi = 0; qi < BQ; qi++) {
+                        const float* qq = qh + (size_t)qi * hd + e;
+#pragma unroll
+                        for (int z = 0; z < VEC; z++) acc[qi] = fmaf(qq[z], kf[z], acc[qi]);
+                    }
                 }
             }
 #pragma unroll
@@ -259,6 +292,7 @@ talking_attention_kernel(TalkParams p) {
             float acc[BQ];
 #pragma unroll
             for (int qi = 0; qi < BQ; qi++) acc[qi] = 0.f;
+#pragma unroll 8
             for (int kj = 0; kj < bk; kj++) {
                 const float v = to_float(vc[(size_t)kj * row_k]);
 #pragma unroll
@@ -272,6 +306,11 @@ talking_attention_kernel(TalkParams p) {
         }
     }
     __syncthreads();
+    if (split) {
+        for (int i = threadIdx.x; i < hd; i += TALK_THREADS) my_o[i] = O[i];
+        for (int i = threadIdx.x; i < H; i += TALK_THREADS) { my_ml[i] = run_m[i]; my_ml[H + i] = run_l[i]; }
+        return;
+    }
     const T* gate = p.gate ? (const T*)p.gate + (size_t)(tok0 + q0) * p.ldg : nullptr;
     for (int i = threadIdx.x; i < nq * hd; i += TALK_THREADS) {
         const int qi = i / hd, e = i - qi * hd;
@@ -279,6 +318,54 @@ talking_attention_kernel(TalkParams p) {
         float v = l > 0.f ? O[i] / l : 0.f;
         if (gate) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)qi * p.ldg + e])));
         out[i] = from_float<T>(v);
+    }
+}
+
+// What the splits of a decode step left, folded: with M_h = max(sink_h, the splits' maxima),
+//   out[e] = sum_s exp(m_s - M) O_s[e] / (exp(sink_h - M) + sum_s exp(m_s - M) l_s)  [* sigmoid(gate[e])],   h = the head of entry e.
+// A block a sequence; the splits are added in their order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+talk_merge_kernel(T* __restrict__ out, const T* __restrict__ gate, long ldg, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                  const float* __restrict__ sink, const int* __restrict__ slot_ids, const int* __restrict__ cu_seqlens, int heads, int d,
+                  int max_splits) {
+    extern __shared__ float wsm[];      // [max_splits][heads] weights, then [heads] 1 / denominators
+    pdl_wait();
+    pdl_launch_dependents();
+    const int b = blockIdx.x, hd = heads * d;
+    const int tok = cu_seqlens[b];
+    if (cu_seqlens[b + 1] - tok <= 0) return;      // (a sequence without a token in this step)
+    T* o = out + (size_t)tok * hd;
+    if (slot_ids[b] < 0) {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) o[i] = from_float<T>(0.f);
+        return;
+    }
+    const float* ml = part_ml + (size_t)b * max_splits * 2 * heads;
+    float* inv = wsm + max_splits * heads;
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        float M = sink ? sink[h] : -INFINITY;
+        for (int s = 0; s < max_splits; s++) M = fmaxf(M, ml[(size_t)s * 2 * heads + h]);
+        float den = (sink && M != -INFINITY) ? expf(sink[h] - M) : 0.f;
+        for (int s = 0; s < max_splits; s++) {
+            const float m = ml[(size_t)s * 2 * heads + h];
+            const float w = (m == -INFINITY || M == -INFINITY) ? 0.f : expf(m - M);
+            wsm[s * heads + h] = w;
+            den = fmaf(w, ml[(size_t)s * 2 * heads + heads + h], den);
+        }
+        inv[h] = den > 0.f ? 1.0f / den : 0.f;
+    }
+    __syncthreads();
+    const float* po = part_o + (size_t)b * max_splits * hd;
+    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+        const int h = e / d;
+        float v = 0.f;
+        for (int s = 0; s < max_splits; s++) {
+            const float w = wsm[s * heads + h];
+            if (w != 0.f) v = fmaf(w, po[(size_t)s * hd + e], v);     // (a split without keys left nothing to read)
+        }
+        v *= inv[h];
+        if (gate) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)tok * ldg + e])));
+        o[e] = from_float<T>(v);
     }
 }
 
@@ -294,7 +381,12 @@ cudaError_t talk_launch(const TalkParams& p, int max_new_tokens, int batch, size
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(kernel, dim3((max_new_tokens + BQ - 1) / BQ, batch), dim3(TALK_THREADS), smem, stream, p);
+    const int tiles = p.split_keys > 0 ? p.max_splits : (max_new_tokens + BQ - 1) / BQ;
+    cudaError_t e = launch_pdl(kernel, dim3(tiles, batch), dim3(TALK_THREADS), smem, stream, p);
+    if (e != cudaSuccess || p.split_keys == 0) return e;
+    const size_t msm = sizeof(float) * ((size_t)p.max_splits * p.heads + p.heads);
+    return launch_pdl(talk_merge_kernel<T>, dim3(batch), dim3(256), msm, stream, (T*)p.out, (const T*)p.gate, p.ldg, (const float*)p.part_o,
+                      (const float*)p.part_ml, p.sink, p.slot_ids, p.cu_seqlens, p.heads, p.d, p.max_splits);
 }
 
 }  // namespace
@@ -318,10 +410,12 @@ HYMT2_API int hymt2_talking_attention(void* out, const void* q, const void* gate
                                       const int* block_table, int table_stride, int block_tokens, const int* cu_seqlens,
                                       const int* slot_ids, const int* kv_lens, int batch, int max_new_tokens, int heads, int kv_heads,
                                       int d, float scale, const float* talk, const float* temp, const float* sink, int mask_kind,
-                                      int mask_size, cudaStream_t stream) {
+                                      int mask_size, int split_keys, int max_splits, float* part_o, float* part_ml, cudaStream_t stream) {
     if (batch == 0 || max_new_tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && batch <= 65535 && max_new_tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0,
                   "talking_attention: bad sizes");
+    HYMT2_REQUIRE(split_keys == 0 || (max_new_tokens == 1 && max_splits > 0 && max_splits <= 65535 && part_o && part_ml && split_keys % 32 == 0),
+                  "talking_attention: splits are for steps of one token a sequence, in whole key tiles, with room for their sums");
     HYMT2_REQUIRE(mask_kind == MASK_NONE || (mask_size > 0 && (mask_kind == MASK_CHUNK || mask_kind == MASK_WINDOW)),
                   "talking_attention: mask kind %d with size %d", mask_kind, mask_size);
     HYMT2_REQUIRE(block_tokens > 0, "talking_attention: block_tokens must be positive");
@@ -350,6 +444,8 @@ HYMT2_API int hymt2_talking_attention(void* out, const void* q, const void* gate
     p.slot_ids = slot_ids; p.kv_lens = kv_lens; p.talk = talk; p.temp = temp; p.sink = sink; p.ldg = ldg; p.table_stride = table_stride;
     p.block_tokens = block_tokens; p.heads = heads; p.kv_heads = kv_heads; p.d = d; p.mask_kind = mask_kind; p.mask_size = mask_size;
     p.bk = bk; p.scale = scale;
+    p.split_keys = split_keys; p.max_splits = max_splits; p.part_o = part_o; p.part_ml = part_ml;
+    HYMT2_REQUIRE(split_keys == 0 || (bq == 1 && split_keys % bk == 0), "talking_attention: splits of %d keys do not fit tiles of %d", split_keys, bk);
     cudaError_t e = cudaSuccess;
 #define TALK_GO(T, V)                                                                           \
     do {                                                                                        \

@@ -1692,6 +1692,7 @@ def talk_prep(x: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None
                                   _ptr(inv_freq), c_int(rot_dims), c_int(T), c_int(heads), c_int(kv_heads), c_int(d), _stream()), "talk_prep")
 
 
+TALK_SPLIT_KEYS = 128     # decode steps: keys a block (four tiles); a constant
 TALK_MMA_MIN_TOKENS = 8   # a sequence's new tokens from which a step's attention runs 16 queries a block on the tensor cores
 _talk_mma_ok: dict = {}
 
@@ -1706,11 +1707,13 @@ def talking_attention_mma_supported(heads: int, kv_heads: int, d: int, block_tok
 def talking_attention(out: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | None, k_plane: torch.Tensor, v_plane: torch.Tensor,
                       block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
                       max_new_tokens: int, heads: int, kv_heads: int, d: int, scale: float, talk: torch.Tensor, temp: torch.Tensor,
-                      sink: torch.Tensor | None, mask: str | None, mask_size: int) -> None:
+                      sink: torch.Tensor | None, mask: str | None, mask_size: int, max_kv_len: int = 0) -> None:
     """Attention of the new tokens over the paged cache with the heads' scores mixed before the softmax:
     s_h = sum_g talk[h, g] * temp[g] * scale * (q_g . k_g); a sink per head in the denominator (or None); mask None (causal),
     "chunk" (only keys of the query's own chunk of mask_size positions) or "window" (the last mask_size); the output times
-    sigmoid(gate) entry by entry where a gate [T, heads * d] is given.  float32 scores and softmax."""
+    sigmoid(gate) entry by entry where a gate [T, heads * d] is given.  float32 scores and softmax.  `max_kv_len` (an upper bound
+    of the sequences' lengths; 0: unknown): a decode step whose queries may see more than TALK_SPLIT_KEYS keys cuts them into
+    splits of that many (a constant, so that the cut depends on nothing else), a block each, and folds them in split order."""
     _need(out, "out", None, 2); _need(q, "q", out.dtype, 2); _need(k_plane, "k_plane", out.dtype, 4); _need(v_plane, "v_plane", out.dtype, 4)
     T = out.shape[0]
     if out.shape[1] != heads * d or q.shape != out.shape or k_plane.shape[1] != kv_heads or k_plane.shape[3] != d or v_plane.shape != k_plane.shape:
@@ -1735,11 +1738,18 @@ def talking_attention(out: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | N
                                                   c_float(scale), _ptr(talk), _ptr(temp), _ptr(sink), c_int(MASKS[mask]), c_int(mask_size),
                                                   _stream()), "talking_attention_mma")
         return
+    split, max_splits, part_o, part_ml = 0, 0, None, None
+    span = min(max_kv_len, mask_size + 31) if mask is not None else max_kv_len       # (the first tile may start up to 31 keys early)
+    if max_new_tokens == 1 and span > TALK_SPLIT_KEYS and k_plane.shape[2] % 32 == 0:
+        split, max_splits = TALK_SPLIT_KEYS, -(-(span + 31) // TALK_SPLIT_KEYS)
+        part_o = torch.empty(batch * max_splits * heads * d, dtype=torch.float32, device=out.device)
+        part_ml = torch.empty(batch * max_splits * 2 * heads, dtype=torch.float32, device=out.device)
     _check(_lib().hymt2_talking_attention(_ptr(out), _ptr(q), _ptr(gate), c_long(ldg), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(out.dtype)),
                                           _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens),
                                           _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(max_new_tokens), c_int(heads), c_int(kv_heads),
                                           c_int(d), c_float(scale), _ptr(talk), _ptr(temp), _ptr(sink), c_int(MASKS[mask]),
-                                          c_int(mask_size), _stream()), "talking_attention")
+                                          c_int(mask_size), c_int(split), c_int(max_splits), _ptr(part_o), _ptr(part_ml), _stream()),
+           "talking_attention", 2 if split else 1)
 
 
 # -- the gated delta rule ----------------------------------------------------------------------------------------------------------

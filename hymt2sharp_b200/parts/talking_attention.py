@@ -109,7 +109,8 @@ class TalkingAttention:
         out = torch.empty((T, H * d), dtype=proj.dtype, device=proj.device)
         gate = proj[:, qk:qk + H * d] if self.names["g"] is not None else None
         ops.talking_attention(out, q, gate, k_plane, v_plane, table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
-                              ctx.max_new_tokens, H, G, d, self.scale, self.talk, self.temp, self.sink, self.mask, self.mask_size)
+                              ctx.max_new_tokens, H, G, d, self.scale, self.talk, self.temp, self.sink, self.mask, self.mask_size,
+                              max_kv_len=ctx.max_kv_len)
         if store:
             self.out_store(out, out=residual)
             ctx.prenormed = None

@@ -353,6 +353,7 @@ def _talk_reference(x, w, heads, kv_heads, dim, scale, size, dims):
     (64, 4, 1, 32, 4, 100, 32, True, False),        # one key head for all heads; chunks that straddle blocks; no gate
     (128, 2, 2, 64, 2, None, 32, False, True),      # no mask, no sink: plain causal softmax with mixed scores
     (64, 1, 1, 8, 0, 33, 0, True, True),            # one head (nothing to mix), no convolution, no rotation
+    (64, 4, 2, 16, 2, 200, 8, True, True),          # chunks long enough that a decode step cuts its keys into splits
     (128, 16, 4, 128, 4, 48, 64, True, True),       # wide: fewer queries a block
 ])
 def test_talking_attention_in_prompts_portions_decoding_and_batches(dtype, hidden, heads, kv_heads, dim, taps, size, dims, sink, gate):
