@@ -231,7 +231,13 @@ talking_attention_kernel(TalkParams p) {
                 for (int e = 0; e < d; e += VEC) {
                     const Pack<T, VEC> kv = load_pack<T, VEC>(kr + e);
 #pragma unroll
-                    for (int z = 0; z < VEC; z++) part[z] = fmaf(qh[e + z], to_float(kv.v[z]), part[z]);
+                    for (int z = 0; z < VEC; z += 4) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qh + e + z);      // (Q rows start on 16 bytes; VEC is 4 or 8)
+                        part[z] = fmaf(q4.x, to_float(kv.v[z]), part[z]);
+                        part[z + 1] = fmaf(q4.y, to_float(kv.v[z + 1]), part[z + 1]);
+                        part[z + 2] = fmaf(q4.z, to_float(kv.v[z + 2]), part[z + 2]);
+                        part[z + 3] = fmaf(q4.w, to_float(kv.v[z + 3]), part[z + 3]);
+                    }
                 }
 #pragma unroll
                 for (int z = 0; z < VEC; z++) acc[0] += part[z];
@@ -284,24 +290,55 @@ talking_attention_kernel(TalkParams p) {
             }
         }
         __syncthreads();
-        // -- O = alpha O + P V: an item is (head, value entry); a value is read once for all BQ queries
-        for (int item = threadIdx.x; item < hd; item += TALK_THREADS) {
-            const int h = item / d, c = item - h * d;
-            const T* vc = Vt + (size_t)(h / rep) * d + c;
-            const float* ph = s_mix + (size_t)h * bk;
-            float acc[BQ];
+        // -- O = alpha O + P V.  Few queries a block: an item is (head, VEC neighbouring value entries), read in one access a key;
+        //    many: an item is (head, value entry), a value read once for all BQ queries
+        if constexpr (VEC > 1 && BQ * VEC <= 32) {
+            for (int item = threadIdx.x; item < hd / VEC; item += TALK_THREADS) {
+                const int e0 = item * VEC, h = e0 / d, c = e0 - h * d;
+                const T* vc = Vt + (size_t)(h / rep) * d + c;
+                const float* ph = s_mix + (size_t)h * bk;
+                float acc[BQ][VEC];
 #pragma unroll
-            for (int qi = 0; qi < BQ; qi++) acc[qi] = 0.f;
-#pragma unroll 8
-            for (int kj = 0; kj < bk; kj++) {
-                const float v = to_float(vc[(size_t)kj * row_k]);
+                for (int qi = 0; qi < BQ; qi++)
 #pragma unroll
-                for (int qi = 0; qi < BQ; qi++) acc[qi] = fmaf(ph[(size_t)qi * H * bk + kj], v, acc[qi]);
+                    for (int z = 0; z < VEC; z++) acc[qi][z] = 0.f;
+#pragma unroll 4
+                for (int kj = 0; kj < bk; kj++) {
+                    const Pack<T, VEC> vv = load_pack<T, VEC>(vc + (size_t)kj * row_k);
+#pragma unroll
+                    for (int qi = 0; qi < BQ; qi++) {
+                        const float pw = ph[(size_t)qi * H * bk + kj];
+#pragma unroll
+                        for (int z = 0; z < VEC; z++) acc[qi][z] = fmaf(pw, to_float(vv.v[z]), acc[qi][z]);
+                    }
+                }
+#pragma unroll
+                for (int qi = 0; qi < BQ; qi++) {
+                    float* o = O + (size_t)qi * hd + e0;
+                    const float a = alpha[qi * H + h];
+#pragma unroll
+                    for (int z = 0; z < VEC; z++) o[z] = o[z] * a + acc[qi][z];
+                }
             }
+        } else {
+            for (int item = threadIdx.x; item < hd; item += TALK_THREADS) {
+                const int h = item / d, c = item - h * d;
+                const T* vc = Vt + (size_t)(h / rep) * d + c;
+                const float* ph = s_mix + (size_t)h * bk;
+                float acc[BQ];
 #pragma unroll
-            for (int qi = 0; qi < BQ; qi++) {
-                float* o = O + (size_t)qi * hd + item;
-                *o = *o * alpha[qi * H + h] + acc[qi];
+                for (int qi = 0; qi < BQ; qi++) acc[qi] = 0.f;
+#pragma unroll 8
+                for (int kj = 0; kj < bk; kj++) {
+                    const float v = to_float(vc[(size_t)kj * row_k]);
+#pragma unroll
+                    for (int qi = 0; qi < BQ; qi++) acc[qi] = fmaf(ph[(size_t)qi * H * bk + kj], v, acc[qi]);
+                }
+#pragma unroll
+                for (int qi = 0; qi < BQ; qi++) {
+                    float* o = O + (size_t)qi * hd + item;
+                    *o = *o * alpha[qi * H + h] + acc[qi];
+                }
             }
         }
     }
