@@ -216,13 +216,14 @@ def rutetar_config(size: str, layers: int):
 
 # Pulenex: of every four layers the first is latent attention in a sliding window, the second retention with rotated q and k and
 # no feed-forward, the third runs chunked attention whose heads talk and the gated delta rule side by side, and the fourth is
-# latent attention that reads the first one's compressed rows; the feed-forward is dense, gated and clamped
+# latent attention that reads the first one's compressed rows; the feed-forward is dense, gated and clamped.  The chunks do
+# not divide the prompt lengths that the lists use, so that a decode step finds its query a third of the way into a chunk
 PULENEX_SIZES = {
     "s": dict(width=1024, vocab=32768, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, window=1024, ret_heads=8, ret_dim=128, ret_vdim=128,
-              talk_heads=8, talk_kv_heads=2, talk_dim=128, chunk=1024, delta_heads=8, delta_kv_heads=4, delta_dim=128, delta_vdim=128,
+              talk_heads=8, talk_kv_heads=2, talk_dim=128, chunk=768, delta_heads=8, delta_kv_heads=4, delta_dim=128, delta_vdim=128,
               ranks=64, taps=4, ff=2816, dense=DESIGN_SIZES["s"]["dense"]),
     "m": dict(width=2048, vocab=65536, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=2048, ret_heads=16, ret_dim=128, ret_vdim=128,
-              talk_heads=16, talk_kv_heads=4, talk_dim=128, chunk=2048, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
+              talk_heads=16, talk_kv_heads=4, talk_dim=128, chunk=1536, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
               ranks=64, taps=4, ff=5632, dense=DESIGN_SIZES["m"]["dense"]),
 }
 PULENEX_ORDER = ["latent", "retention", "parallel", "latent_from"]   # repeated up to --layers

@@ -81,7 +81,29 @@ __global__ void layernorm_add_norm_kernel(float* __restrict__ y, const float* __
 // row is read once and the passes do not wait for memory again.
 constexpr int LN_PER = 8;
 
-template <typename TX, typename TW, typename TY, bool ADD>
+// entry j of a thread's LN_PER: with V = 4 a thread's entries are two runs of four neighbours (16-byte accesses of float32 rows)
+template <int V> __device__ __forceinline__ int ln_index(int j) {
+    return V == 1 ? (int)(threadIdx.x + j * blockDim.x) : (int)(((j / 4) * blockDim.x + threadIdx.x) * 4 + (j % 4));
+}
+template <int V> __device__ __forceinline__ void ln_load(const float* __restrict__ src, int dim, float v[LN_PER]) {
+    if constexpr (V == 4) {
+#pragma unroll
+        for (int r = 0; r < LN_PER / 4; r++) {
+            const int i = (r * blockDim.x + threadIdx.x) * 4;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < dim) x = *reinterpret_cast<const float4*>(src + i);
+            v[4 * r] = x.x; v[4 * r + 1] = x.y; v[4 * r + 2] = x.z; v[4 * r + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < LN_PER; j++) {
+            const int i = ln_index<1>(j);
+            v[j] = i < dim ? src[i] : 0.f;
+        }
+    }
+}
+
+template <typename TX, typename TW, typename TY, bool ADD, int V = 1>
 __global__ void layernorm_cached_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
                                         const int* __restrict__ rows_index, int dim, float eps, float out_scale) {
     __shared__ float scratch[33];
@@ -90,17 +112,21 @@ __global__ void layernorm_cached_kernel(TY* __restrict__ y, const TX* __restrict
     const int r = blockIdx.x;
     const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim;
     float v[LN_PER], s = 0.f;
+    if constexpr (V == 4) ln_load<4>((const float*)src, dim, v);
+    else {
 #pragma unroll
-    for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
-        v[j] = i < dim ? to_float(src[i]) : 0.f;
-        s += v[j];
+        for (int j = 0; j < LN_PER; j++) {
+            const int i = ln_index<1>(j);
+            v[j] = i < dim ? to_float(src[i]) : 0.f;
+        }
     }
+#pragma unroll
+    for (int j = 0; j < LN_PER; j++) s += v[j];
     const float mean = block_sum(s, scratch) / (float)dim;
     float q = 0.f;
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         const float d = i < dim ? v[j] - mean : 0.f;
         q = fmaf(d, d, q);
     }
@@ -108,7 +134,7 @@ __global__ void layernorm_cached_kernel(TY* __restrict__ y, const TX* __restrict
     TY* dst = y + (size_t)r * dim;
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         if (i < dim) {
             float o = (v[j] - mean) * scale * to_float(gain[i]);
             if (out_scale != 1.0f) o *= out_scale;
@@ -118,7 +144,7 @@ __global__ void layernorm_cached_kernel(TY* __restrict__ y, const TX* __restrict
     }
 }
 
-template <typename TW, typename TH>
+template <typename TW, typename TH, int V = 1>
 __global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const float* __restrict__ x, const TW* __restrict__ gain_a,
                                                  TH* __restrict__ h, const TW* __restrict__ gain_b, int dim, float eps_a, float eps_b) {
     __shared__ float scratch[33];
@@ -126,18 +152,15 @@ __global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const fl
     pdl_launch_dependents();
     const size_t off = (size_t)blockIdx.x * dim;
     float v[LN_PER], old[LN_PER], s = 0.f;
+    ln_load<V>(x + off, dim, v);
+    ln_load<V>(y + off, dim, old);
 #pragma unroll
-    for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
-        v[j] = i < dim ? x[off + i] : 0.f;
-        old[j] = i < dim ? y[off + i] : 0.f;
-        s += v[j];
-    }
+    for (int j = 0; j < LN_PER; j++) s += v[j];
     const float mean = block_sum(s, scratch) / (float)dim;
     float q = 0.f;
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         const float d = i < dim ? v[j] - mean : 0.f;
         q = fmaf(d, d, q);
     }
@@ -145,7 +168,7 @@ __global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const fl
     float s2 = 0.f;
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         if (i < dim) {
             v[j] = old[j] + (v[j] - mean) * scale_a * to_float(gain_a[i]);
             y[off + i] = v[j];
@@ -155,7 +178,7 @@ __global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const fl
     if (gain_b == nullptr) {
 #pragma unroll
         for (int j = 0; j < LN_PER; j++) {
-            const int i = threadIdx.x + j * blockDim.x;
+            const int i = ln_index<V>(j);
             if (i < dim) h[off + i] = from_float<TH>(v[j]);
         }
         return;
@@ -164,14 +187,14 @@ __global__ void layernorm_add_norm_cached_kernel(float* __restrict__ y, const fl
     float q2 = 0.f;
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         const float d = i < dim ? v[j] - mean_b : 0.f;
         q2 = fmaf(d, d, q2);
     }
     const float scale_b = 1.0f / sqrtf(block_sum(q2, scratch) / (float)dim + eps_b);
 #pragma unroll
     for (int j = 0; j < LN_PER; j++) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = ln_index<V>(j);
         if (i < dim) h[off + i] = from_float<TH>((v[j] - mean_b) * scale_b * to_float(gain_b[i]));
     }
 }
@@ -229,6 +252,18 @@ HYMT2_API int hymt2_layernorm(void* y, int y_dtype, const void* x, int x_dtype, 
     HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
     HYMT2_REQUIRE(!add || y_dtype == HYMT2_F32, "layernorm: adding into the output needs float32 rows");
     if (const int ct = cached_threads(dim)) {
+        if (x_dtype == HYMT2_F32 && dim % 4 == 0 && (uintptr_t)x % 16 == 0 && ct * LN_PER >= dim) {   // 16-byte reads of float32 rows
+            HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
+                if (add) {
+                    launch_pdl(layernorm_cached_kernel<float, TW, float, true, 4>, dim3(rows), dim3(ct), 0, stream, (float*)y, (const float*)x,
+                               (const TW*)gain, rows_index, dim, eps, out_scale);
+                } else {
+                    HYMT2_DISPATCH_DTYPE(y_dtype, TY, (launch_pdl(layernorm_cached_kernel<float, TW, TY, false, 4>, dim3(rows), dim3(ct), 0, stream,
+                                                                  (TY*)y, (const float*)x, (const TW*)gain, rows_index, dim, eps, out_scale)));
+                }
+            });
+            return hymt2_check_launch("layernorm");
+        }
         HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
             if (add) {
                 launch_pdl(layernorm_cached_kernel<TX, TW, float, true>, dim3(rows), dim3(ct), 0, stream, (float*)y, (const TX*)x, (const TW*)gain,
@@ -258,9 +293,15 @@ HYMT2_API int hymt2_layernorm_add_norm(float* y, const float* x, const void* gai
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && dim > 0, "layernorm: bad sizes rows=%d dim=%d", rows, dim);
     if (const int ct = cached_threads(dim)) {
-        HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
-            (launch_pdl(layernorm_add_norm_cached_kernel<TW, TH>, dim3(rows), dim3(ct), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
-                        (const TW*)gain_b, dim, eps_a, eps_b))));
+        if (dim % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+            HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
+                (launch_pdl(layernorm_add_norm_cached_kernel<TW, TH, 4>, dim3(rows), dim3(ct), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
+                            (const TW*)gain_b, dim, eps_a, eps_b))));
+        } else {
+            HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
+                (launch_pdl(layernorm_add_norm_cached_kernel<TW, TH>, dim3(rows), dim3(ct), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
+                            (const TW*)gain_b, dim, eps_a, eps_b))));
+        }
         return hymt2_check_launch("layernorm_add_norm");
     }
     HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
