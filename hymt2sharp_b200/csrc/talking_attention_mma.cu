@@ -19,7 +19,7 @@ namespace {
 using namespace nvcuda;
 typedef __nv_bfloat16 bf16;
 
-constexpr int TM_THREADS = 256, TM_WARPS = 8, TM_BQ = 16, TM_BK = 32, TM_MAXH = 16, TM_SLD = TM_BK + 4, TM_PLD = TM_BK + 8, TM_XLD = 20;
+constexpr int TM_BQ = 16, TM_BK = 32, TM_MAXH = 16, TM_SLD = TM_BK + 4, TM_PLD = TM_BK + 8, TM_XLD = 20;
 enum { TM_MASK_NONE = 0, TM_MASK_CHUNK = 1, TM_MASK_WINDOW = 2 };
 
 struct TalkMmaParams {
@@ -56,15 +56,16 @@ __device__ __forceinline__ int tm_lowest_seen(int pos, int kind, int size) {
     return 0;
 }
 
-size_t tm_smem_bytes(int H, int G, int d) {
+size_t tm_smem_bytes(int H, int G, int d, int warps) {
     const size_t ldq = (size_t)H * d + 8, ldk = (size_t)G * d + 8;
-    return 2 * (TM_BQ * ldq + 2 * TM_BK * ldk + (size_t)H * TM_BQ * TM_PLD) + 4 * ((size_t)H * TM_BQ * TM_SLD + TM_WARPS * 16 * TM_XLD + (size_t)H * TM_MAXH + 3 * (size_t)H * TM_BQ) + 128;
+    return 2 * (TM_BQ * ldq + 2 * TM_BK * ldk + (size_t)H * TM_BQ * TM_PLD) + 4 * ((size_t)H * TM_BQ * TM_SLD + (size_t)warps * 16 * TM_XLD + (size_t)H * TM_MAXH + 3 * (size_t)H * TM_BQ) + 128;
 }
 
 // MAXF: the most output fragments (a head's 16 queries x 16 value entries) that a warp holds
-template <int MAXF>
+template <int MAXF, int TM_THREADS>
 __global__ void __launch_bounds__(TM_THREADS)
 talking_attention_mma_kernel(TalkMmaParams p) {
+    constexpr int TM_WARPS = TM_THREADS / 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     pdl_wait();
     pdl_launch_dependents();
@@ -148,12 +149,13 @@ talking_attention_mma_kernel(TalkMmaParams p) {
     auto ask_tile = [&](bf16* dst, const bf16* cache, int k0) {
         if (k0 <= pos_last) {
             const int block = table[k0 / p.block_tokens], off = k0 % p.block_tokens;
-            const int kj = tid >> 3, pos = k0 + kj;
+            constexpr int PER_ROW = TM_THREADS / TM_BK;          // threads that share a key row
+            const int kj = tid / PER_ROW, pos = k0 + kj;
             const bool live_row = pos >= lo && pos <= pos_last && block >= 0;
             for (int g = 0; g < G; g++) {
                 const bf16* src = cache + (((size_t)(live_row ? block : 0) * G + g) * p.block_tokens + off + kj) * d;
                 bf16* row = dst + kj * ldk + g * d;
-                for (int x = (tid & 7) * 8; x < d; x += 64) tm_copy16(row + x, src + x, live_row);
+                for (int x = (tid % PER_ROW) * 8; x < d; x += PER_ROW * 8) tm_copy16(row + x, src + x, live_row);
             }
         }
         tm_commit();
@@ -165,24 +167,43 @@ talking_attention_mma_kernel(TalkMmaParams p) {
         ask_tile(Vs, p.v_cache, k0);
         tm_wait_but_one();  // the keys of this pass are here (the values may still be on their way)
         __syncthreads();
-        // -- raw scores: a warp takes a head, both halves of the key tile share the head's query fragments
-        for (int h = warp; h < H; h += TM_WARPS) {
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
-            wmma::fill_fragment(s0, 0.f);
-            wmma::fill_fragment(s1, 0.f);
-            const bf16* qh = Qs + h * d;
-            const bf16* kh = Ks + (h / rep) * d;
-            for (int ks = 0; ks < dblocks; ks++) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
-                wmma::load_matrix_sync(a, qh + ks * 16, ldq);
-                wmma::load_matrix_sync(b0, kh + ks * 16, ldk);
-                wmma::load_matrix_sync(b1, kh + 16 * ldk + ks * 16, ldk);
-                wmma::mma_sync(s0, a, b0, s0);
-                wmma::mma_sync(s1, a, b1, s1);
+        // -- raw scores: with eight warps a warp takes a head and both halves of the key tile share the head's query fragments;
+        //    with sixteen a warp takes one half of a head's tile
+        if constexpr (TM_WARPS <= 8) {
+            for (int h = warp; h < H; h += TM_WARPS) {
+                wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
+                wmma::fill_fragment(s0, 0.f);
+                wmma::fill_fragment(s1, 0.f);
+                const bf16* qh = Qs + h * d;
+                const bf16* kh = Ks + (h / rep) * d;
+                for (int ks = 0; ks < dblocks; ks++) {
+                    wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                    wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
+                    wmma::load_matrix_sync(a, qh + ks * 16, ldq);
+                    wmma::load_matrix_sync(b0, kh + ks * 16, ldk);
+                    wmma::load_matrix_sync(b1, kh + 16 * ldk + ks * 16, ldk);
+                    wmma::mma_sync(s0, a, b0, s0);
+                    wmma::mma_sync(s1, a, b1, s1);
+                }
+                wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD, s0, TM_SLD, wmma::mem_row_major);
+                wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD + 16, s1, TM_SLD, wmma::mem_row_major);
             }
-            wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD, s0, TM_SLD, wmma::mem_row_major);
-            wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD + 16, s1, TM_SLD, wmma::mem_row_major);
+        } else {
+            for (int item = warp; item < 2 * H; item += TM_WARPS) {
+                const int h = item >> 1, kb = item & 1;
+                wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0;
+                wmma::fill_fragment(s0, 0.f);
+                const bf16* qh = Qs + h * d;
+                const bf16* kh = Ks + (h / rep) * d + kb * 16 * ldk;
+                for (int ks = 0; ks < dblocks; ks++) {
+                    wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                    wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0;
+                    wmma::load_matrix_sync(a, qh + ks * 16, ldq);
+                    wmma::load_matrix_sync(b0, kh + ks * 16, ldk);
+                    wmma::mma_sync(s0, a, b0, s0);
+                }
+                wmma::store_matrix_sync(Ss + (size_t)h * TM_BQ * TM_SLD + kb * 16, s0, TM_SLD, wmma::mem_row_major);
+            }
         }
         __syncthreads();
         ask_tile(Ks, p.k_cache, k0 + TM_BK);   // the key tile is free: the keys of the next pass (or an empty group behind the last pass)
@@ -295,14 +316,14 @@ talking_attention_mma_kernel(TalkMmaParams p) {
     }
 }
 
-template <int MAXF>
+template <int MAXF, int THREADS>
 cudaError_t tm_launch(const TalkMmaParams& p, int max_new_tokens, int batch, size_t smem, cudaStream_t stream) {
-    auto kernel = talking_attention_mma_kernel<MAXF>;
+    auto kernel = talking_attention_mma_kernel<MAXF, THREADS>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(kernel, dim3((max_new_tokens + TM_BQ - 1) / TM_BQ, batch), dim3(TM_THREADS), smem, stream, p);
+    return launch_pdl(kernel, dim3((max_new_tokens + TM_BQ - 1) / TM_BQ, batch), dim3(THREADS), smem, stream, p);
 }
 
 }  // namespace
@@ -311,10 +332,10 @@ cudaError_t tm_launch(const TalkMmaParams& p, int max_new_tokens, int batch, siz
 // blocks in whole key tiles, and everything of a block within the shared memory
 HYMT2_API int hymt2_talking_attention_mma_supported(int heads, int kv_heads, int d, int block_tokens) {
     if (heads < 1 || heads > TM_MAXH || kv_heads < 1 || heads % kv_heads || d < 16 || d % 16 || block_tokens % TM_BK) return 0;
-    if ((heads * (d / 16) + TM_WARPS - 1) / TM_WARPS > 16) return 0;
+    if ((heads * (d / 16) + 7) / 8 > 16) return 0;
     int dev = 0, limit = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-    return tm_smem_bytes(heads, kv_heads, d) <= (size_t)limit ? 1 : 0;
+    return tm_smem_bytes(heads, kv_heads, d, 8) <= (size_t)limit ? 1 : 0;
 }
 
 HYMT2_API int hymt2_talking_attention_mma(void* out, const void* q, const void* gate, long ldg, const void* k_cache, const void* v_cache,
@@ -333,13 +354,25 @@ HYMT2_API int hymt2_talking_attention_mma(void* out, const void* q, const void* 
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens; p.talk = talk; p.temp = temp;
     p.sink = sink; p.ldg = ldg; p.table_stride = table_stride; p.block_tokens = block_tokens; p.heads = heads; p.kv_heads = kv_heads; p.d = d;
     p.mask_kind = mask_kind; p.mask_size = mask_size; p.scale = scale;
-    const size_t smem = tm_smem_bytes(heads, kv_heads, d);
-    const int per_warp = (heads * (d / 16) + TM_WARPS - 1) / TM_WARPS;
+    // sixteen warps a block where there is work for them (32 output fragments or more, at most 8 a warp) and room in the shared
+    // memory; else eight
+    const int frags = heads * (d / 16);
+    int dev = 0, limit = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    const bool wide = frags >= 32 && (frags + 15) / 16 <= 8 && tm_smem_bytes(heads, kv_heads, d, 16) <= (size_t)limit;
+    const int warps = wide ? 16 : 8;
+    const size_t smem = tm_smem_bytes(heads, kv_heads, d, warps);
+    const int per_warp = (frags + warps - 1) / warps;
     cudaError_t e;
-    if (per_warp <= 2) e = tm_launch<2>(p, max_new_tokens, batch, smem, stream);
-    else if (per_warp <= 4) e = tm_launch<4>(p, max_new_tokens, batch, smem, stream);
-    else if (per_warp <= 8) e = tm_launch<8>(p, max_new_tokens, batch, smem, stream);
-    else e = tm_launch<16>(p, max_new_tokens, batch, smem, stream);
+    if (wide) {
+        if (per_warp <= 2) e = tm_launch<2, 512>(p, max_new_tokens, batch, smem, stream);
+        else if (per_warp <= 4) e = tm_launch<4, 512>(p, max_new_tokens, batch, smem, stream);
+        else e = tm_launch<8, 512>(p, max_new_tokens, batch, smem, stream);
+    } else if (per_warp <= 2) e = tm_launch<2, 256>(p, max_new_tokens, batch, smem, stream);
+    else if (per_warp <= 4) e = tm_launch<4, 256>(p, max_new_tokens, batch, smem, stream);
+    else if (per_warp <= 8) e = tm_launch<8, 256>(p, max_new_tokens, batch, smem, stream);
+    else e = tm_launch<16, 256>(p, max_new_tokens, batch, smem, stream);
     if (e != cudaSuccess) { hymt2_set_error("talking_attention_mma: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("talking_attention_mma");
 }
